@@ -1,0 +1,382 @@
+"""Benchmark of the vector-wise N:M sparse GEMM hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one multiply C = A.B of the square workload (M = K = 4096, 4096
+columns of B per GPU, 8:32 sparsity, V = 32, FP32) with the operands resident in
+HBM.  With N > 1 (one process per GPU under torch.distributed.run) the columns
+of B are sharded by vector groups, 4096 per rank, A replicated: weak scaling,
+no data-path collective.  Rank 0 prints one JSON line.
+
+* ``value``         useful TFLOP/s = 2.M.N_total.W / t, max over ranks of the device time
+* ``roofline``      of the FP32 kernel: useful FLOPs against the FFMA rate measured live
+                    on the same GPU (register-only kernel), with the HBM time beside it
+* ``e2e``           the same metric through the host-buffer entry point
+                    (nmspmm_gemm_host): H2D of A, B and the raw indices, index packing,
+                    multiply, D2H of C inside the timed region
+* ``cpu_baseline``  the reference's host multiply timed on this box's cores on a
+                    bounded row sample (N = 1, rank 0)
+* ``per_ratio``     the same step for 16:32, 12:32, 8:32, 4:32 (useful and
+                    dense-equivalent TFLOP/s, roofline fraction)
+
+``--impl reference`` times the reference's own CPU implementation of the path
+(oracle/_ref, compiled unchanged from the reference's sources; the C restatement
+when that object is absent) on the same workload, each step a bounded row sample.
+"""
+from __future__ import annotations
+
+import argparse
+import contextlib
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M_SQ = N_SQ = K_SQ = 4096
+HEADLINE_KEEP = 8
+SETS = 3                      # operand sets rotated between steps (3 x 144 MB > 126 MB of L2)
+METRIC = "useful TFLOP/s, vector-wise N:M SpMM, 4096^3 8:32 V=32 FP32"
+
+# DRAM bytes per launch of the headline kernel from the ncu capture summarised in
+# profiles/ (null until a capture exists for the exact kernel and workload).
+NCU_TRAFFIC_BYTES = {"nm_gemm_ffma_kernel<128,128,64,16,high> 4096^3 8:32": None}
+
+
+def algorithmic_bytes(M, N, K, n_keep, layout_ns=128):
+    """Compulsory traffic of one multiply: A, compressed B, indices, C once each,
+    plus column_info on the high-sparsity path."""
+    W = K // 32 * n_keep
+    b = 4 * (M * K + W * N + W * N // 32 + M * N)
+    if n_keep in (8, 4):
+        b += 4 * (N // layout_ns) * (W // (2 * n_keep)) * 64
+    return b
+
+
+@contextlib.contextmanager
+def quiet_stdout():
+    """The reference's host multiply printf()s its thread count; keep stdout to the JSON line."""
+    sys.stdout.flush()
+    saved = os.dup(1)
+    devnull = os.open(os.devnull, os.O_WRONLY)
+    os.dup2(devnull, 1)
+    try:
+        yield
+    finally:
+        os.dup2(saved, 1)
+        os.close(saved)
+        os.close(devnull)
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while a region runs."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.sm_max = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.sm_max = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nv = None
+
+    def sample(self):
+        if self._nv is None:
+            return
+        try:
+            self.samples.append(int(self._nv.nvmlDeviceGetClockInfo(self._h, self._nv.NVML_CLOCK_SM)))
+            mask = int(self._nv.nvmlDeviceGetCurrentClocksEventReasons(self._h))
+            for bit, name in self.REASONS.items():
+                if mask & bit:
+                    self.reasons.add(name)
+        except Exception:
+            pass
+
+    def __enter__(self):
+        def loop():
+            while not self._stop.is_set():
+                self.sample()
+                self._stop.wait(0.005)
+        self._stop.clear()
+        self._thread = threading.Thread(target=loop, daemon=True)
+        self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.sm_max,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def physical_gpu_index(local_rank: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except Exception:
+            pass
+    return local_rank
+
+
+# ------------------------------------------------------------------------------------
+# CPU side: the reference's host multiply on a bounded sample.
+# ------------------------------------------------------------------------------------
+
+def cpu_reference_impl():
+    import oracle
+    if oracle.have_reference():
+        return oracle.reference(), "reference"
+    return oracle.restatement(), "port"
+
+
+def cpu_sample(pkg, impl, p, rows: int):
+    """Times the host multiply on the first ``rows`` rows of A (rows are independent
+    in the reference's loop nest).  Returns seconds."""
+    sub = np.ascontiguousarray(p.A_km[:, :rows])
+    B_col, D_col = p.B_col, p.D_col
+    with quiet_stdout():
+        t0 = time.perf_counter()
+        impl.nm_gemm_f32(sub, B_col, D_col)
+        return time.perf_counter() - t0
+
+
+def rows_for_budget(pkg, impl, p, cores: int, seconds: float) -> int:
+    """Rows of A whose host multiply takes about ``seconds`` (calibrated on a warm probe)."""
+    probe_rows = min(p.M, 4 * cores)
+    cpu_sample(pkg, impl, p, probe_rows)
+    t = cpu_sample(pkg, impl, p, probe_rows)
+    rows = int(min(p.M, max(cores, probe_rows * seconds / max(t, 1e-6))))
+    return max(cores, rows // cores * cores)
+
+
+def cpu_baseline(pkg, p, budget_s: float = 12.0):
+    impl, kind = cpu_reference_impl()
+    cores = impl.num_threads()
+    rows = rows_for_budget(pkg, impl, p, cores, budget_s)
+    t = cpu_sample(pkg, impl, p, rows)
+    flops = 2.0 * rows * p.N * p.W
+    return {"value": flops / t / 1e12, "unit": "useful TFLOP/s", "cores": cores, "kind": kind,
+            "sample": f"first {rows} of {p.M} rows of A against the full B ({p.N} columns, W={p.W}); "
+                      f"{t:.2f} s of nmGEMM_on_cpu", "seconds": t}
+
+
+def run_reference_arm(args, rank: int, world: int):
+    if rank != 0:
+        return
+    from __graft_entry__ import load_package
+    pkg = load_package(native=False)
+    impl, kind = cpu_reference_impl()
+    cores = impl.num_threads()
+    p = pkg.formats.make_random(M_SQ, N_SQ, K_SQ, HEADLINE_KEEP, seed=0)
+    total_budget = 60.0                              # seconds of CPU work over warm-up + steps
+    rows = rows_for_budget(pkg, impl, p, cores, total_budget / max(1, args.steps + args.warmup))
+    for _ in range(args.warmup):
+        cpu_sample(pkg, impl, p, rows)
+    times = [cpu_sample(pkg, impl, p, rows) for _ in range(args.steps)]
+    sec = float(np.mean(times))
+    value = 2.0 * rows * p.N * p.W / sec / 1e12
+    sample = f"each step: first {rows} of {p.M} rows of A against the full B, all {cores} host threads"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded)",
+        "config": {"workload": "square 4096^3, 8:32, V=32, FP32 (reference's CPU multiply nmGEMM_on_cpu)",
+                   "M": M_SQ, "N": N_SQ, "K": K_SQ, "n_keep": HEADLINE_KEEP},
+        "cpu_baseline": {"value": value, "unit": "useful TFLOP/s", "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------
+# GPU side.
+# ------------------------------------------------------------------------------------
+
+def time_steps(torch, fn, steps: int, barrier=None):
+    """Device time of ``steps`` calls of fn(i) on the current stream, in ms."""
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if barrier:
+        barrier()
+    torch.cuda.synchronize()
+    start.record()
+    for i in range(steps):
+        fn(i)
+    end.record()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    return start.elapsed_time(end)
+
+
+def run_ours(args, rank: int, world: int, local_rank: int):
+    import torch
+    import torch.distributed as dist
+
+    from __graft_entry__ import load_package
+    pkg = load_package(native=True)
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # This rank's column shard: 4096 columns of B (its own seed), A shared by all ranks.
+    M, K, n_local = M_SQ, K_SQ, N_SQ
+    p = pkg.formats.make_random(M, n_local, K, HEADLINE_KEEP, seed=0)
+    if rank != 0:
+        q = pkg.formats.make_random(4, n_local, K, HEADLINE_KEEP, seed=1000 + rank)
+        p.BT, p.DT = q.BT, q.DT
+    op = pkg.NMSpMM.from_problem(p, layout_ns=128)
+    A_sets = [torch.from_numpy(p.A_km).cuda()]
+    for s in range(1, SETS):
+        A_sets.append(torch.roll(A_sets[0], s * 131, dims=1).contiguous())
+    C_sets = [torch.empty((M, n_local), dtype=torch.float32, device="cuda") for _ in range(SETS)]
+    desc = op.desc(M)
+    plan = pkg.plan(desc)
+
+    def step(i):
+        op.matmul(A_sets[i % SETS], out=C_sets[i % SETS])
+
+    for i in range(max(3, args.warmup)):
+        step(i)
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    with sampler:
+        ms = time_steps(torch, step, args.steps, barrier)
+        sampler.sample()
+    ms = max_over_ranks(ms)
+    if pkg.device_status() != 0:
+        raise RuntimeError("a device-side bounded wait gave up during the timed region")
+    ms_per_step = ms / args.steps
+    useful = 2.0 * M * n_local * p.W
+    value = world * useful / (ms_per_step * 1e-3) / 1e12
+
+    # ---- roofline of the dominant (only) kernel, per GPU --------------------------
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    hbm_gbs = float(peaks.get("hbm_gbs", 6650.0))
+    hbm_src = "MEASURED_PEAKS.json" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
+    ffma_peak = pkg.measure_ffma_peak()
+    abytes = algorithmic_bytes(M, n_local, K, HEADLINE_KEEP)
+    t_flop = useful / (ffma_peak * 1e12)
+    t_mem = abytes / (hbm_gbs * 1e9)
+    achieved = useful / (ms_per_step * 1e-3) / 1e12
+    roofline = {
+        "bound": "fp32_simt" if t_flop >= t_mem else "hbm",
+        "achieved": achieved, "peak": ffma_peak, "unit": "TFLOP/s", "frac": max(t_flop, t_mem) / (ms_per_step * 1e-3),
+        "traffic": NCU_TRAFFIC_BYTES.get("nm_gemm_ffma_kernel<128,128,64,16,high> 4096^3 8:32"),
+        "peak_source": "FFMA rate measured live on this GPU by the library's register-only kernel "
+                       "(nominal 148 SMs x 128 lanes x 2 x SM clock)",
+        "algorithmic_bytes": abytes, "algorithmic_flops": useful,
+        "hbm_time_us": t_mem * 1e6, "hbm_peak_gbs": hbm_gbs, "hbm_peak_source": hbm_src,
+        "kernel": f"nm_gemm_ffma_kernel tile {plan.tile_m}x{plan.tile_n}, split_k {plan.split_k}, "
+                  f"{plan.stages} stages, {plan.smem_bytes} B smem, grid {plan.grid_x}x{plan.grid_y}x{plan.grid_z}",
+        "kernel_ms": ms_per_step,
+    }
+
+    # ---- the other ratios (N=1 only, short) ---------------------------------------
+    per_ratio = []
+    if world == 1:
+        for n_keep in (16, 12, 8, 4):
+            pr = p if n_keep == HEADLINE_KEEP else pkg.formats.make_random(M, n_local, K, n_keep, seed=0)
+            opr = op if n_keep == HEADLINE_KEEP else pkg.NMSpMM.from_problem(pr, layout_ns=128)
+            fn = lambda i, o=opr: o.matmul(A_sets[i % SETS], out=C_sets[i % SETS])
+            for i in range(3):
+                fn(i)
+            t = time_steps(torch, fn, 20) / 20
+            uf = 2.0 * M * n_local * pr.W
+            tf, tm = uf / (ffma_peak * 1e12), algorithmic_bytes(M, n_local, K, n_keep) / (hbm_gbs * 1e9)
+            per_ratio.append({"n_keep": n_keep, "path": "fp32", "ms": t, "useful_tflops": uf / (t * 1e-3) / 1e12,
+                              "dense_equivalent_tflops": 2.0 * M * n_local * K / (t * 1e-3) / 1e12,
+                              "roofline_frac": max(tf, tm) / (t * 1e-3)})
+
+    # ---- end to end through the host-buffer entry point ------------------------------
+    hA = torch.from_numpy(p.A_km).pin_memory()
+    hB = torch.from_numpy(p.BT).pin_memory()
+    hD = torch.from_numpy(p.DT).pin_memory()
+    hC = torch.empty((M, n_local), dtype=torch.float32).pin_memory()
+    e2e_steps = max(3, min(args.steps, 10))
+
+    def e2e_step(i):
+        pkg.gemm_host(desc, hA, hB, hD, hC, on_current_stream=True)
+
+    for i in range(3):
+        e2e_step(i)
+    e2e_ms = max_over_ranks(time_steps(torch, e2e_step, e2e_steps, barrier)) / e2e_steps
+    h2d = hA.numel() * 4 + hB.numel() * 4 + hD.numel() * 4
+    d2h = hC.numel() * 4
+    e2e = {"value": world * useful / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+           "call": "nmspmm_gemm_host (pinned host A, B, raw indices -> packed on the GPU -> multiply -> host C)"}
+    # parity of what the e2e call returned, against the resident-operand result
+    e2e_err = float((hC.cuda() - C_sets[0].copy_(op.matmul(A_sets[0]))).norm() / C_sets[0].norm())
+
+    cpu = cpu_baseline(pkg, p) if (world == 1 and rank == 0) else None
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded splitmix64: A, kept values U[-1,1), "
+                                                       "random sorted indices)",
+            "config": {"workload": "square 4096^3, 8:32 (75 %), V=32, FP32 exact path", "M": M, "K": K,
+                       "N_per_gpu": n_local, "N_total": n_local * world, "n_keep": HEADLINE_KEEP, "layout_ns": 128,
+                       "parallelism": f"B column-vector groups sharded over {world} GPU(s), A replicated, no collective",
+                       "l2": f"operands rotate over {SETS} sets of A and C (3 x 128 MB > 126 MB L2); no flush"},
+            "dense_equivalent_tflops": world * 2.0 * M * n_local * K / (ms_per_step * 1e-3) / 1e12,
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "e2e_rel_err_vs_resident": e2e_err,
+            "gpu_launches": args.steps, "clocks": sampler.summary(), "per_ratio": per_ratio,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

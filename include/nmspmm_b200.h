@@ -1,0 +1,163 @@
+/*
+ * nmspmm_b200 -- C-ABI of the sm_100a vector-wise N:M sparse GEMM library.
+ *
+ * C(M x N) = A(M x K) . B(K x N); B keeps `n_keep` rows out of every window of
+ * 32 consecutive k, and 32 adjacent columns of B (one "vector") share the list
+ * of kept rows.  Operand formats are the reference's (include/utils.h:10-66 of
+ * M-H482/NM-SpMM):
+ *
+ *   A            col-major, A[i + k*M]                      float
+ *   B            row-major compressed values, B[w*N + j]    float, W = K/32*n_keep rows
+ *   DT           row-major [W][Q] window-local k (0..31)    int,   Q = N/32
+ *   D            DT after packing: [N/Ns][W][Ns/32]         int
+ *   column_info  high-sparsity path only: per (Ns block, 64-k window) the
+ *                ascending list of used local columns, -1 padded to 64
+ *   C            row-major, C[i*N + j]                      float
+ *
+ * Every function returns an nmspmm_status.  Pointers named *_dev are device
+ * pointers, *_host are host pointers; all must be 16-byte aligned.  `stream` is a
+ * cudaStream_t passed as void* (NULL = the legacy default stream).  Nothing here
+ * allocates device memory except the functions that say so.
+ *
+ * The C++ entry points with the reference's exact names and signatures
+ * (include/NM-SpMM.h of this repository) are thin wrappers over these.
+ */
+#ifndef NMSPMM_B200_H
+#define NMSPMM_B200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum nmspmm_status {
+    NMSPMM_OK = 0,
+    NMSPMM_INVALID_ARGUMENT = 1,   /* null / misaligned pointer, shape not divisible as required */
+    NMSPMM_UNSUPPORTED = 2,        /* N:M ratio or layout outside the supported families */
+    NMSPMM_CUDA_ERROR = 3,         /* a CUDA runtime call failed; see nmspmm_last_cuda_error() */
+    NMSPMM_WORKSPACE_TOO_SMALL = 4,
+    NMSPMM_DEVICE_TIMEOUT = 5      /* a bounded device-side wait gave up (status word set by the kernel) */
+} nmspmm_status;
+
+/* Arithmetic of the gathered mini-GEMM. */
+typedef enum nmspmm_path {
+    NMSPMM_PATH_FP32 = 0,          /* exact FP32 FFMA, register tiled */
+    NMSPMM_PATH_TF32 = 1           /* tcgen05 kind::tf32, FP32 accumulation in TMEM */
+} nmspmm_path;
+
+/* Index format of D (selected in the reference by which entry point is called). */
+typedef enum nmspmm_format {
+    NMSPMM_FORMAT_LOW = 0,         /* D holds window-local k (window = 32); no column_info.
+                                      Replaces PreProcessing_low_sparsity + *_low_sparsity launchers. */
+    NMSPMM_FORMAT_HIGH = 1         /* D holds ranks into column_info (window = 64).
+                                      Replaces transIndex + PreProcessing_high_sparsity + *_high_sparsity. */
+} nmspmm_format;
+
+const char* nmspmm_status_string(int status);
+/* Last CUDA error code (cudaError_t as int) seen by this thread inside the library. */
+int nmspmm_last_cuda_error(void);
+/* Library version, 0xMMmmpp. */
+int nmspmm_version(void);
+
+/* ------------------------------------------------------------------ index packing
+ * Device-pointer forms: one hand-written kernel each, bit-exact with the reference's
+ * host loops.  They are out of place (DT_dev is read, D_dev is written; the two must
+ * not overlap) so that the packing can be timed alone. */
+
+/* Replaces transIndex (src/preprocessing.cu:3-15): rows of every odd 32-window get
+ * +pruning_M, in place.  The caller doubles its own pruning_N / pruning_M afterwards. */
+int nmspmm_trans_index_device(int* DT_dev, int W, int Q, int pruning_N, int pruning_M, void* stream);
+
+/* Replaces PreProcessing_low_sparsity (src/preprocessing.cu:80-100): [W][Q] -> [Q/Qs][W][Qs]. */
+int nmspmm_preprocess_low_device(const int* DT_dev, int* D_dev, int W, int Q, int Ns, void* stream);
+
+/* Replaces PreProcessing_high_sparsity (src/preprocessing.cu:17-78).  DT_dev holds
+ * merged-window indices (0..pruning_M-1, i.e. after trans_index); pruning_M <= 64.
+ * Writes D_dev (ranks, re-tiled) and (N/Ns)*(W/pruning_N)*pruning_M ints of
+ * column_info_dev.  With fuse_trans_index != 0, DT_dev holds the raw 0..31 indices,
+ * pruning_N / pruning_M are the un-doubled values and the merge of window pairs is
+ * done on the fly (DT_dev is not modified).  column_info_tail_ints further ints
+ * after the last list are set to -1 (pass pruning_M for the reference driver's
+ * extra window, 0 to leave them alone). */
+int nmspmm_preprocess_high_device(const int* DT_dev, int* D_dev, int* column_info_dev,
+                                  int pruning_M, int pruning_N, int W, int Q, int Ns,
+                                  int fuse_trans_index, int column_info_tail_ints, void* stream);
+
+/* Host-pointer forms with the reference's in-place semantics (H2D + kernel + D2H;
+ * they allocate and free temporary device buffers).  The extra column_info window
+ * is left untouched, like the reference. */
+int nmspmm_trans_index_host(int* DT_host, int W, int N, int Q, int* pruning_N, int* pruning_M);
+int nmspmm_preprocess_low_host(int* DT_host, int W, int Q, int Ns);
+int nmspmm_preprocess_high_host(int* column_info_host, int pruning_M, int pruning_N,
+                                int* DT_host, int W, int Q, int N, int Ns);
+
+/* ------------------------------------------------------------------ the multiply */
+
+typedef struct nmspmm_gemm_desc {
+    int M, N, K;
+    int n_keep;        /* kept rows per 32-window: 32, 16, 12 (LOW) / 8, 4 (HIGH); LOW also takes 8 */
+    int format;        /* nmspmm_format */
+    int layout_ns;     /* Ns the index buffers were packed for: 32, 64 or 128 */
+    int path;          /* nmspmm_path */
+    int split_k;       /* >=1: number of K slices; 0: chosen by the library */
+    int tile;          /* 0: chosen by the library; otherwise an nmspmm_tile id (testing / tuning) */
+} nmspmm_gemm_desc;
+
+/* Bytes of scratch the multiply needs for this description (0 when split_k resolves to 1).
+ * The scratch holds split-K partial tiles and per-tile arrival counters; the counters
+ * must be zero before the first use (cudaMemset once) and are left zero by every call. */
+size_t nmspmm_gemm_workspace_bytes(const nmspmm_gemm_desc* desc);
+
+/* Replaces the eight nmGEMM_*_matrices_{low,high}_sparsity launchers
+ * (src/kernel_*.cu).  C is overwritten with A.B for every split_k (deterministic:
+ * partials are summed in slice order by the last tile to arrive).  Asynchronous on
+ * `stream`.  column_info_dev is NULL for NMSPMM_FORMAT_LOW. */
+int nmspmm_gemm(const nmspmm_gemm_desc* desc,
+                const float* A_dev, const float* B_dev, const int* D_dev, const int* column_info_dev,
+                float* C_dev, void* workspace_dev, size_t workspace_bytes, void* stream);
+
+/* Same, with scratch that the library allocates on first use and keeps per host thread
+ * (cudaMalloc inside the first call that needs it).  For callers bound to the
+ * reference's launcher signatures, which carry no workspace argument. */
+int nmspmm_gemm_with_cached_workspace(const nmspmm_gemm_desc* desc,
+                                      const float* A_dev, const float* B_dev, const int* D_dev,
+                                      const int* column_info_dev, float* C_dev, void* stream);
+
+/* Reads the device status word that kernels raise when a bounded wait gives up
+ * (synchronises the device).  Returns NMSPMM_OK or NMSPMM_DEVICE_TIMEOUT; the raw
+ * word goes to *status_out when non-NULL; clear != 0 resets it. */
+int nmspmm_device_status(int* status_out, int clear);
+
+/* What the library resolved for a description (filled by nmspmm_gemm_plan). */
+typedef struct nmspmm_gemm_plan_info {
+    int tile;          /* nmspmm_tile id */
+    int tile_m, tile_n;
+    int split_k;
+    int grid_x, grid_y, grid_z;
+    int threads;
+    int smem_bytes;
+    int stages;
+} nmspmm_gemm_plan_info;
+int nmspmm_gemm_plan(const nmspmm_gemm_desc* desc, nmspmm_gemm_plan_info* out);
+
+/* End-to-end form on HOST buffers: copies A, B, the raw DT [W][Q] and nothing else
+ * to the device, packs the indices there, multiplies and copies C back.  Device
+ * buffers are kept in a per-thread arena that grows on demand (this function
+ * allocates).  Work is issued on `stream` (NULL = a private stream of the arena) and
+ * the function returns after that stream has drained.  This is what a caller of the
+ * reference's test driver does around its launcher (tests/test_nmspmm.cu:72-101). */
+int nmspmm_gemm_host(const nmspmm_gemm_desc* desc,
+                     const float* A_host, const float* B_host, const int* DT_host, float* C_host,
+                     void* stream);
+/* Frees the arena of nmspmm_gemm_host and the wrappers' cached scratch. */
+int nmspmm_release_cached(void);
+
+/* Sustained FFMA rate of this GPU in TFLOP/s (2 flops per FFMA), measured with a
+ * register-only kernel on `stream` (synchronous).  The FP32 roofline denominator. */
+int nmspmm_measure_ffma_peak(double* tflops_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NMSPMM_B200_H */

@@ -1,0 +1,515 @@
+// C-ABI of the library (include/nmspmm_b200.h): argument checks, plan selection
+// (tile + split-K), scratch layout, and the host-buffer convenience forms.
+#include <cuda_runtime.h>
+#include <mutex>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "kernels.h"
+#include "nmspmm_b200.h"
+
+namespace nmspmm {
+
+#define NMSPMM_VARIANT_TABLE(name)           \
+    extern const FfmaVariant kFfma_##name[]; \
+    extern const int kFfma_##name##_count;
+NMSPMM_VARIANT_TABLE(low32)
+NMSPMM_VARIANT_TABLE(low16)
+NMSPMM_VARIANT_TABLE(low12)
+NMSPMM_VARIANT_TABLE(low8)
+NMSPMM_VARIANT_TABLE(high16)
+NMSPMM_VARIANT_TABLE(high8)
+
+const FfmaVariant* find_ffma_variant(int tile_id, int ws, int mode)
+{
+    struct Table { const FfmaVariant* v; int n; };
+    const Table tables[] = { { kFfma_low32, kFfma_low32_count }, { kFfma_low16, kFfma_low16_count },
+                             { kFfma_low12, kFfma_low12_count }, { kFfma_low8, kFfma_low8_count },
+                             { kFfma_high16, kFfma_high16_count }, { kFfma_high8, kFfma_high8_count } };
+    for (const Table& t : tables)
+        for (int i = 0; i < t.n; ++i)
+            if (t.v[i].tile_id == tile_id && t.v[i].ws == ws && t.v[i].mode == mode) return &t.v[i];
+    return nullptr;
+}
+
+static thread_local int tl_last_cuda_error = 0;
+
+static int cuda_fail(cudaError_t e)
+{
+    tl_last_cuda_error = static_cast<int>(e);
+    return NMSPMM_CUDA_ERROR;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---- per-device facts ---------------------------------------------------------
+struct DeviceInfo {
+    bool known = false;
+    int sms = 0;
+    int* status_word = nullptr;
+};
+static DeviceInfo g_dev[64];
+static std::mutex g_dev_mutex;
+__device__ int g_status_word;      // raised by kernels whose bounded waits gave up
+
+static int device_info(DeviceInfo** out)
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (dev < 0 || dev >= 64) return NMSPMM_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    DeviceInfo& d = g_dev[dev];
+    if (!d.known) {
+        e = cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return cuda_fail(e);
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&d.status_word), g_status_word);
+        if (e != cudaSuccess) return cuda_fail(e);
+        e = cudaMemset(d.status_word, 0, sizeof(int));
+        if (e != cudaSuccess) return cuda_fail(e);
+        d.known = true;
+    }
+    *out = &d;
+    return NMSPMM_OK;
+}
+
+// ---- plan -----------------------------------------------------------------------
+struct Plan {
+    const FfmaVariant* v = nullptr;
+    int W = 0, ws = 0, n_win = 0, split_k = 1;
+    dim3 grid;
+    size_t counters_bytes = 0, partial_bytes = 0;
+};
+
+static int check_desc(const nmspmm_gemm_desc* d, int* ws_out, int* mode_out)
+{
+    if (!d) return NMSPMM_INVALID_ARGUMENT;
+    if (d->M <= 0 || d->N <= 0 || d->K <= 0) return NMSPMM_INVALID_ARGUMENT;
+    if (d->M % 4 != 0 || d->N % kVecLenHost != 0 || d->K % 32 != 0) return NMSPMM_INVALID_ARGUMENT;
+    if (d->layout_ns != 32 && d->layout_ns != 64 && d->layout_ns != 128) return NMSPMM_INVALID_ARGUMENT;
+    if (d->N % d->layout_ns != 0) return NMSPMM_INVALID_ARGUMENT;
+    if (d->split_k < 0) return NMSPMM_INVALID_ARGUMENT;
+    if (d->format == NMSPMM_FORMAT_LOW) {
+        if (d->n_keep != 32 && d->n_keep != 16 && d->n_keep != 12 && d->n_keep != 8) return NMSPMM_UNSUPPORTED;
+        *ws_out = d->n_keep;
+        *mode_out = kModeLow;
+    } else if (d->format == NMSPMM_FORMAT_HIGH) {
+        if (d->n_keep != 8 && d->n_keep != 4) return NMSPMM_UNSUPPORTED;
+        if (d->K % 64 != 0) return NMSPMM_INVALID_ARGUMENT;
+        *ws_out = 2 * d->n_keep;
+        *mode_out = kModeHigh;
+    } else {
+        return NMSPMM_INVALID_ARGUMENT;
+    }
+    return NMSPMM_OK;
+}
+
+static int pick_tile(const nmspmm_gemm_desc* d, int mode)
+{
+    if (mode == kModeHigh && d->layout_ns == 64) return kTile128x64;    // a tile must sit inside one index block
+    if (mode == kModeHigh && d->layout_ns == 32) return kTile128x32;
+    if (d->M <= 16) return kTile16x128;
+    if (d->M <= 32) return kTile32x128;
+    if (d->M <= 64) return kTile64x128;
+    const int pad128 = (d->M + 127) / 128 * 128, pad64 = (d->M + 63) / 64 * 64;
+    return (pad64 < pad128) ? kTile64x128 : kTile128x128;
+}
+
+static int make_plan(const nmspmm_gemm_desc* d, int sms, Plan* p)
+{
+    int ws = 0, mode = 0;
+    int rc = check_desc(d, &ws, &mode);
+    if (rc != NMSPMM_OK) return rc;
+    if (d->path != NMSPMM_PATH_FP32) return NMSPMM_UNSUPPORTED;
+    const int tile = d->tile ? d->tile : pick_tile(d, mode);
+    const FfmaVariant* v = find_ffma_variant(tile, ws, mode);
+    if (!v) return NMSPMM_UNSUPPORTED;
+    if (mode == kModeHigh && (d->layout_ns % v->ns) != 0) return NMSPMM_UNSUPPORTED;
+    p->v = v;
+    p->ws = ws;
+    p->W = d->K / 32 * d->n_keep;
+    p->n_win = p->W / ws;
+    const int gx = (d->N + v->ns - 1) / v->ns, gy = (d->M + v->ms - 1) / v->ms;
+    if (gy > 65535) return NMSPMM_UNSUPPORTED;
+    int split = d->split_k;
+    if (split == 0) {
+        // Fill the machine: as many slices as leave every resident CTA slot one unit of
+        // work, but at least four windows per slice.
+        const long long tiles = static_cast<long long>(gx) * gy;
+        const long long slots = static_cast<long long>(sms > 0 ? sms : 148) * v->min_blocks;
+        long long s = slots / tiles;
+        if (s < 1) s = 1;
+        const long long cap = p->n_win / 4 > 0 ? p->n_win / 4 : 1;
+        if (s > cap) s = cap;
+        if (s > 64) s = 64;
+        split = static_cast<int>(s);
+    }
+    if (split > p->n_win) split = p->n_win;
+    if (split < 1) split = 1;
+    if (split > 65535) return NMSPMM_UNSUPPORTED;
+    p->split_k = split;
+    p->grid = dim3(gx, gy, split);
+    if (split > 1) {
+        const size_t tiles = static_cast<size_t>(gx) * gy;
+        p->counters_bytes = (tiles * sizeof(unsigned) + 255) / 256 * 256;
+        p->partial_bytes = tiles * split * static_cast<size_t>(v->ms) * v->ns * sizeof(float);
+    }
+    return NMSPMM_OK;
+}
+
+static int sm_count()
+{
+    DeviceInfo* di = nullptr;
+    return device_info(&di) == NMSPMM_OK ? di->sms : 148;
+}
+
+// ---- cached scratch for the entry points whose signature has no workspace ---------
+struct Scratch {
+    void* ptr = nullptr;
+    size_t bytes = 0;
+    int device = -1;
+};
+static thread_local Scratch tl_scratch;
+
+static int scratch_reserve(size_t bytes, void** out)
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e);
+    Scratch& s = tl_scratch;
+    if (s.device != dev || s.bytes < bytes) {
+        if (s.ptr) {
+            cudaDeviceSynchronize();
+            cudaFree(s.ptr);
+            s.ptr = nullptr;
+            s.bytes = 0;
+        }
+        size_t want = bytes < (size_t(8) << 20) ? (size_t(8) << 20) : bytes;
+        e = cudaMalloc(&s.ptr, want);
+        if (e != cudaSuccess) return cuda_fail(e);
+        e = cudaMemset(s.ptr, 0, want);
+        if (e != cudaSuccess) return cuda_fail(e);
+        s.bytes = want;
+        s.device = dev;
+    }
+    *out = s.ptr;
+    return NMSPMM_OK;
+}
+
+// ---- arena of nmspmm_gemm_host ---------------------------------------------------
+struct Arena {
+    void* ptr = nullptr;
+    size_t bytes = 0;
+    int device = -1;
+    cudaStream_t stream = nullptr;
+};
+static thread_local Arena tl_arena;
+
+static int arena_reserve(size_t bytes, unsigned char** out, cudaStream_t* st)
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e);
+    Arena& a = tl_arena;
+    if (a.device != dev || a.bytes < bytes) {
+        if (a.ptr) {
+            cudaDeviceSynchronize();
+            cudaFree(a.ptr);
+            a.ptr = nullptr;
+            a.bytes = 0;
+        }
+        e = cudaMalloc(&a.ptr, bytes);
+        if (e != cudaSuccess) return cuda_fail(e);
+        a.bytes = bytes;
+        if (a.device != dev || !a.stream) {
+            e = cudaStreamCreateWithFlags(&a.stream, cudaStreamNonBlocking);
+            if (e != cudaSuccess) return cuda_fail(e);
+        }
+        a.device = dev;
+    }
+    *out = static_cast<unsigned char*>(a.ptr);
+    *st = a.stream;
+    return NMSPMM_OK;
+}
+
+static size_t round256(size_t b) { return (b + 255) / 256 * 256; }
+
+}  // namespace nmspmm
+
+using namespace nmspmm;
+
+extern "C" {
+
+const char* nmspmm_status_string(int status)
+{
+    switch (status) {
+    case NMSPMM_OK: return "ok";
+    case NMSPMM_INVALID_ARGUMENT: return "invalid argument";
+    case NMSPMM_UNSUPPORTED: return "unsupported N:M ratio, layout or path";
+    case NMSPMM_CUDA_ERROR: return "CUDA runtime error";
+    case NMSPMM_WORKSPACE_TOO_SMALL: return "workspace too small";
+    case NMSPMM_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
+    default: return "unknown status";
+    }
+}
+
+int nmspmm_last_cuda_error(void) { return tl_last_cuda_error; }
+int nmspmm_version(void) { return 0x000100; }
+
+int nmspmm_trans_index_device(int* DT_dev, int W, int Q, int pruning_N, int pruning_M, void* stream)
+{
+    if (!DT_dev || W < 0 || Q <= 0 || pruning_N <= 0 || pruning_M <= 0) return NMSPMM_INVALID_ARGUMENT;
+    if (W % (2 * pruning_N) != 0) return NMSPMM_INVALID_ARGUMENT;      // window pairs must be whole
+    cudaError_t e = launch_trans_index(DT_dev, W, Q, pruning_N, pruning_M, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? NMSPMM_OK : cuda_fail(e);
+}
+
+int nmspmm_preprocess_low_device(const int* DT_dev, int* D_dev, int W, int Q, int Ns, void* stream)
+{
+    if (!DT_dev || !D_dev || W < 0 || Q <= 0) return NMSPMM_INVALID_ARGUMENT;
+    if (Ns != 32 && Ns != 64 && Ns != 128) return NMSPMM_INVALID_ARGUMENT;
+    const int Qs = Ns / kVecLenHost;
+    if (Q % Qs != 0) return NMSPMM_INVALID_ARGUMENT;
+    cudaError_t e = launch_retile(DT_dev, D_dev, W, Q, Qs, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? NMSPMM_OK : cuda_fail(e);
+}
+
+int nmspmm_preprocess_high_device(const int* DT_dev, int* D_dev, int* column_info_dev, int pruning_M, int pruning_N,
+                                  int W, int Q, int Ns, int fuse_trans_index, int column_info_tail_ints, void* stream)
+{
+    if (!DT_dev || !D_dev || !column_info_dev || W < 0 || Q <= 0) return NMSPMM_INVALID_ARGUMENT;
+    if (Ns != 32 && Ns != 64 && Ns != 128) return NMSPMM_INVALID_ARGUMENT;
+    const int Qs = Ns / kVecLenHost;
+    if (Q % Qs != 0 || column_info_tail_ints < 0) return NMSPMM_INVALID_ARGUMENT;
+    int pm = pruning_M, pn = pruning_N;
+    if (fuse_trans_index) {
+        pm *= 2;
+        pn *= 2;
+    }
+    if (pn <= 0 || pm <= 0 || pn > pm) return NMSPMM_INVALID_ARGUMENT;
+    if (pm > 64) return NMSPMM_UNSUPPORTED;
+    if (W % pn != 0) return NMSPMM_INVALID_ARGUMENT;
+    cudaError_t e = launch_preprocess_high(DT_dev, D_dev, column_info_dev, pm, pn, W, Q, Qs, fuse_trans_index ? 1 : 0,
+                                           column_info_tail_ints, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? NMSPMM_OK : cuda_fail(e);
+}
+
+// Host-pointer forms: device round trip with the reference's in-place semantics.
+int nmspmm_trans_index_host(int* DT_host, int W, int N, int Q, int* pruning_N, int* pruning_M)
+{
+    (void)N;
+    if (!DT_host || !pruning_N || !pruning_M) return NMSPMM_INVALID_ARGUMENT;
+    const size_t bytes = static_cast<size_t>(W) * Q * sizeof(int);
+    int* d = nullptr;
+    cudaError_t e = cudaMalloc(&d, bytes ? bytes : 4);
+    if (e != cudaSuccess) return cuda_fail(e);
+    int rc = NMSPMM_OK;
+    if ((e = cudaMemcpy(d, DT_host, bytes, cudaMemcpyHostToDevice)) != cudaSuccess) rc = cuda_fail(e);
+    if (rc == NMSPMM_OK) rc = nmspmm_trans_index_device(d, W, Q, *pruning_N, *pruning_M, nullptr);
+    if (rc == NMSPMM_OK && (e = cudaMemcpy(DT_host, d, bytes, cudaMemcpyDeviceToHost)) != cudaSuccess) rc = cuda_fail(e);
+    cudaFree(d);
+    if (rc == NMSPMM_OK) {
+        *pruning_M *= 2;
+        *pruning_N *= 2;
+    }
+    return rc;
+}
+
+int nmspmm_preprocess_low_host(int* DT_host, int W, int Q, int Ns)
+{
+    if (!DT_host) return NMSPMM_INVALID_ARGUMENT;
+    const size_t bytes = static_cast<size_t>(W) * Q * sizeof(int);
+    int* d = nullptr;
+    cudaError_t e = cudaMalloc(&d, 2 * bytes + 4);
+    if (e != cudaSuccess) return cuda_fail(e);
+    int* out = d + static_cast<size_t>(W) * Q;
+    int rc = NMSPMM_OK;
+    if ((e = cudaMemcpy(d, DT_host, bytes, cudaMemcpyHostToDevice)) != cudaSuccess) rc = cuda_fail(e);
+    if (rc == NMSPMM_OK) rc = nmspmm_preprocess_low_device(d, out, W, Q, Ns, nullptr);
+    if (rc == NMSPMM_OK && (e = cudaMemcpy(DT_host, out, bytes, cudaMemcpyDeviceToHost)) != cudaSuccess) rc = cuda_fail(e);
+    cudaFree(d);
+    return rc;
+}
+
+int nmspmm_preprocess_high_host(int* column_info_host, int pruning_M, int pruning_N, int* DT_host, int W, int Q, int N,
+                                int Ns)
+{
+    (void)N;
+    if (!DT_host || !column_info_host || pruning_N <= 0 || Ns <= 0) return NMSPMM_INVALID_ARGUMENT;
+    const size_t n_idx = static_cast<size_t>(W) * Q;
+    const size_t n_ci = static_cast<size_t>(W / pruning_N) * (static_cast<size_t>(Q) * kVecLenHost / Ns) * pruning_M;
+    int* d = nullptr;
+    cudaError_t e = cudaMalloc(&d, (2 * n_idx + n_ci) * sizeof(int) + 4);
+    if (e != cudaSuccess) return cuda_fail(e);
+    int *out = d + n_idx, *ci = out + n_idx;
+    int rc = NMSPMM_OK;
+    if ((e = cudaMemcpy(d, DT_host, n_idx * sizeof(int), cudaMemcpyHostToDevice)) != cudaSuccess) rc = cuda_fail(e);
+    if (rc == NMSPMM_OK) rc = nmspmm_preprocess_high_device(d, out, ci, pruning_M, pruning_N, W, Q, Ns, 0, 0, nullptr);
+    if (rc == NMSPMM_OK && (e = cudaMemcpy(DT_host, out, n_idx * sizeof(int), cudaMemcpyDeviceToHost)) != cudaSuccess)
+        rc = cuda_fail(e);
+    if (rc == NMSPMM_OK && (e = cudaMemcpy(column_info_host, ci, n_ci * sizeof(int), cudaMemcpyDeviceToHost)) != cudaSuccess)
+        rc = cuda_fail(e);
+    cudaFree(d);
+    return rc;
+}
+
+size_t nmspmm_gemm_workspace_bytes(const nmspmm_gemm_desc* desc)
+{
+    Plan p;
+    if (make_plan(desc, sm_count(), &p) != NMSPMM_OK) return 0;
+    return p.counters_bytes + p.partial_bytes;
+}
+
+int nmspmm_gemm_plan(const nmspmm_gemm_desc* desc, nmspmm_gemm_plan_info* out)
+{
+    if (!out) return NMSPMM_INVALID_ARGUMENT;
+    Plan p;
+    int rc = make_plan(desc, sm_count(), &p);
+    if (rc != NMSPMM_OK) return rc;
+    out->tile = p.v->tile_id;
+    out->tile_m = p.v->ms;
+    out->tile_n = p.v->ns;
+    out->split_k = p.split_k;
+    out->grid_x = p.grid.x;
+    out->grid_y = p.grid.y;
+    out->grid_z = p.grid.z;
+    out->threads = p.v->threads;
+    out->smem_bytes = p.v->smem_bytes;
+    out->stages = p.v->stages;
+    return NMSPMM_OK;
+}
+
+int nmspmm_gemm(const nmspmm_gemm_desc* desc, const float* A_dev, const float* B_dev, const int* D_dev,
+                const int* column_info_dev, float* C_dev, void* workspace_dev, size_t workspace_bytes, void* stream)
+{
+    DeviceInfo* di = nullptr;
+    int rc = device_info(&di);
+    if (rc != NMSPMM_OK) return rc;
+    Plan p;
+    rc = make_plan(desc, di->sms, &p);
+    if (rc != NMSPMM_OK) return rc;
+    if (!A_dev || !B_dev || !D_dev || !C_dev) return NMSPMM_INVALID_ARGUMENT;
+    if (desc->format == NMSPMM_FORMAT_HIGH && !column_info_dev) return NMSPMM_INVALID_ARGUMENT;
+    if (!aligned16(A_dev) || !aligned16(B_dev) || !aligned16(D_dev) || !aligned16(C_dev)) return NMSPMM_INVALID_ARGUMENT;
+    GemmArgs a {};
+    a.A = A_dev;
+    a.B = B_dev;
+    a.D = D_dev;
+    a.cinfo = column_info_dev;
+    a.C = C_dev;
+    a.status = di->status_word;
+    a.M = desc->M;
+    a.N = desc->N;
+    a.W = p.W;
+    a.n_win = p.n_win;
+    a.split_k = p.split_k;
+    a.qs_l = desc->layout_ns / kVecLenHost;
+    if (p.split_k > 1) {
+        if (!workspace_dev || !aligned16(workspace_dev)) return NMSPMM_INVALID_ARGUMENT;
+        if (workspace_bytes < p.counters_bytes + p.partial_bytes) return NMSPMM_WORKSPACE_TOO_SMALL;
+        a.counters = static_cast<unsigned*>(workspace_dev);
+        a.partial = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace_dev) + p.counters_bytes);
+    }
+    cudaError_t e = p.v->launch(a, p.grid, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? NMSPMM_OK : cuda_fail(e);
+}
+
+int nmspmm_device_status(int* status_out, int clear)
+{
+    DeviceInfo* di = nullptr;
+    int rc = device_info(&di);
+    if (rc != NMSPMM_OK) return rc;
+    int word = 0;
+    cudaError_t e = cudaMemcpy(&word, di->status_word, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (word != 0 && clear) {
+        e = cudaMemset(di->status_word, 0, sizeof(int));
+        if (e != cudaSuccess) return cuda_fail(e);
+    }
+    if (status_out) *status_out = word;
+    return word == 0 ? NMSPMM_OK : NMSPMM_DEVICE_TIMEOUT;
+}
+
+int nmspmm_gemm_with_cached_workspace(const nmspmm_gemm_desc* desc, const float* A_dev, const float* B_dev,
+                                      const int* D_dev, const int* column_info_dev, float* C_dev, void* stream)
+{
+    const size_t need = nmspmm_gemm_workspace_bytes(desc);
+    void* ws = nullptr;
+    if (need > 0) {
+        int rc = scratch_reserve(need, &ws);
+        if (rc != NMSPMM_OK) return rc;
+    }
+    return nmspmm_gemm(desc, A_dev, B_dev, D_dev, column_info_dev, C_dev, ws, ws ? tl_scratch.bytes : 0, stream);
+}
+
+int nmspmm_gemm_host(const nmspmm_gemm_desc* desc, const float* A_host, const float* B_host, const int* DT_host,
+                     float* C_host, void* stream)
+{
+    if (!A_host || !B_host || !DT_host || !C_host) return NMSPMM_INVALID_ARGUMENT;
+    DeviceInfo* di = nullptr;
+    int rc = device_info(&di);
+    if (rc != NMSPMM_OK) return rc;
+    Plan p;
+    rc = make_plan(desc, di->sms, &p);
+    if (rc != NMSPMM_OK) return rc;
+    const int M = desc->M, N = desc->N, K = desc->K, W = p.W, Q = N / kVecLenHost;
+    const bool high = desc->format == NMSPMM_FORMAT_HIGH;
+    const int pn_m = 2 * desc->n_keep, pm_m = 64;
+    const size_t a_b = round256(sizeof(float) * M * static_cast<size_t>(K));
+    const size_t b_b = round256(sizeof(float) * W * static_cast<size_t>(N));
+    const size_t d_b = round256(sizeof(int) * W * static_cast<size_t>(Q));
+    const size_t c_b = round256(sizeof(float) * M * static_cast<size_t>(N));
+    const size_t ci_b = high ? round256(sizeof(int) * (static_cast<size_t>(W / pn_m) * (N / desc->layout_ns) + 1) * pm_m) : 0;
+    const size_t ws_b = round256(p.counters_bytes + p.partial_bytes);
+    unsigned char* base = nullptr;
+    cudaStream_t st = nullptr;
+    rc = arena_reserve(a_b + b_b + 2 * d_b + c_b + ci_b + ws_b, &base, &st);
+    if (rc != NMSPMM_OK) return rc;
+    if (stream) st = static_cast<cudaStream_t>(stream);
+    float* dA = reinterpret_cast<float*>(base);
+    float* dB = reinterpret_cast<float*>(base + a_b);
+    int* dDT = reinterpret_cast<int*>(base + a_b + b_b);
+    int* dD = reinterpret_cast<int*>(base + a_b + b_b + d_b);
+    float* dC = reinterpret_cast<float*>(base + a_b + b_b + 2 * d_b);
+    int* dCI = reinterpret_cast<int*>(base + a_b + b_b + 2 * d_b + c_b);
+    unsigned char* dWS = base + a_b + b_b + 2 * d_b + c_b + ci_b;
+    cudaError_t e;
+    if ((e = cudaMemcpyAsync(dDT, DT_host, sizeof(int) * W * static_cast<size_t>(Q), cudaMemcpyHostToDevice, st)) != cudaSuccess)
+        return cuda_fail(e);
+    if ((e = cudaMemcpyAsync(dB, B_host, sizeof(float) * W * static_cast<size_t>(N), cudaMemcpyHostToDevice, st)) != cudaSuccess)
+        return cuda_fail(e);
+    if ((e = cudaMemcpyAsync(dA, A_host, sizeof(float) * M * static_cast<size_t>(K), cudaMemcpyHostToDevice, st)) != cudaSuccess)
+        return cuda_fail(e);
+    if (high)
+        rc = nmspmm_preprocess_high_device(dDT, dD, dCI, 32, desc->n_keep, W, Q, desc->layout_ns, 1, pm_m, st);
+    else
+        rc = nmspmm_preprocess_low_device(dDT, dD, W, Q, desc->layout_ns, st);
+    if (rc != NMSPMM_OK) return rc;
+    if (ws_b > 0 && (e = cudaMemsetAsync(dWS, 0, p.counters_bytes, st)) != cudaSuccess) return cuda_fail(e);
+    rc = nmspmm_gemm(desc, dA, dB, dD, high ? dCI : nullptr, dC, ws_b ? dWS : nullptr, ws_b, st);
+    if (rc != NMSPMM_OK) return rc;
+    if ((e = cudaMemcpyAsync(C_host, dC, sizeof(float) * M * static_cast<size_t>(N), cudaMemcpyDeviceToHost, st)) != cudaSuccess)
+        return cuda_fail(e);
+    if ((e = cudaStreamSynchronize(st)) != cudaSuccess) return cuda_fail(e);
+    return nmspmm_device_status(nullptr, 1);
+}
+
+int nmspmm_release_cached(void)
+{
+    cudaDeviceSynchronize();
+    if (tl_scratch.ptr) cudaFree(tl_scratch.ptr);
+    tl_scratch = Scratch();
+    if (tl_arena.ptr) cudaFree(tl_arena.ptr);
+    if (tl_arena.stream) cudaStreamDestroy(tl_arena.stream);
+    tl_arena = Arena();
+    return NMSPMM_OK;
+}
+
+int nmspmm_measure_ffma_peak(double* tflops_out, void* stream)
+{
+    if (!tflops_out) return NMSPMM_INVALID_ARGUMENT;
+    cudaError_t e = measure_ffma_peak(tflops_out, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? NMSPMM_OK : cuda_fail(e);
+}
+
+}  // extern "C"

@@ -1,0 +1,128 @@
+// Device-side building blocks shared by the sm_100a kernels: mbarrier, bulk
+// asynchronous copies (the TMA engine's untiled form) and bounded waits.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace nmspmm {
+
+constexpr int kVecLen = 32;     // columns of B that share one index list (VEC_LEN of the reference API)
+
+// Status word values written by kernels whose bounded waits gave up.
+constexpr int kDevOk = 0;
+constexpr int kDevTimeoutFull = 1;    // a consumer never saw its stage filled
+constexpr int kDevTimeoutEmpty = 2;   // the producer never saw its stage released
+constexpr int kDevTimeoutMma = 3;     // the epilogue never saw the tensor core finish
+
+// Upper bound of one wait, in SM clock cycles (about a second).
+constexpr long long kWaitCycleLimit = 2000000000LL;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p)
+{
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+// Makes freshly initialised barriers visible to the asynchronous proxy.
+__device__ __forceinline__ void mbar_init_fence()
+{
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Waits for the phase with the given parity to complete.  Gives up after
+// kWaitCycleLimit cycles, or as soon as another thread of the CTA has given up
+// (*abort_flag != 0); returns false in both cases and raises the flag.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    unsigned spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 255u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > kWaitCycleLimit) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// Untiled bulk copy global -> shared, completion counted in bytes on an mbarrier.
+// Both addresses 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src_gmem, uint32_t bytes, uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(dst_smem), "l"(src_gmem), "r"(bytes), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ float4 lds128(uint32_t addr)
+{
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ float2 lds64(uint32_t addr)
+{
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ int lds32i(uint32_t addr)
+{
+    int v;
+    asm volatile("ld.shared.s32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+// Which windows (of n_win) slice z of split_k owns: the first n_win % split_k
+// slices get one extra window (the split of src/kernel_64x128_8x8.cu:21-37 of the
+// reference, kept so that a given SPLIT_K covers the same k ranges).
+__host__ __device__ __forceinline__ void slice_range(int n_win, int split_k, int z, int& first, int& count)
+{
+    const int base = n_win / split_k, rem = n_win % split_k;
+    if (z < rem) {
+        count = base + 1;
+        first = z * (base + 1);
+    } else {
+        count = base;
+        first = rem * (base + 1) + (z - rem) * base;
+    }
+}
+
+}  // namespace nmspmm

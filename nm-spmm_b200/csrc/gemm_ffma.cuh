@@ -1,0 +1,344 @@
+// Exact-FP32 vector-wise N:M sparse GEMM for sm_100a.
+//
+// One CTA computes an MS x NS tile of C over a contiguous range of k windows
+// (its split-K slice).  Each window's operands are streamed into a STAGES-deep
+// shared-memory ring with bulk asynchronous copies (the TMA engine), completion
+// counted on mbarriers; the warps take turns issuing a window's copies (a few
+// instructions per warp every NCW windows) and otherwise only compute: there is
+// no CTA-wide barrier in the main loop.  Per window the ring holds
+//     As  [KS][MS]   LOW : the dense 32-k window of A (A is col-major, so k-row r is
+//                          MS contiguous floats)
+//                    HIGH: only the rows listed in column_info for this (Ns block,
+//                          64-k window) -- row r holds A column column_info[r]
+//     Bs  [WS][NS]   the window's compressed rows of B
+//     Ds  [..]       the window's packed indices for the vectors of the tile
+// and the gather of the reference (src/kernel_64x128_8x8.cu:139-159) stays what it
+// was: the shared-memory row address As[D[p]].  Every consumer warp owns one
+// 32-column vector, so that row is warp-uniform, and the 8x8 register tile reads
+// two 128-bit words of A and two of B per 64 FFMAs.
+//
+// split_k > 1: each slice writes its partial tile to scratch; the last slice to
+// arrive (per-tile counter) adds the partials in slice order and writes C, so the
+// result does not depend on arrival order.
+#pragma once
+#include "common.cuh"
+#include "gemm_args.h"
+#include "kernels.h"
+
+namespace nmspmm {
+
+template <int MS, int NS, int WM, int WS, int MODE>
+struct FfmaCfg {
+    static constexpr int KS = (MODE == kModeLow) ? 32 : 64;
+    static constexpr int QT = NS / kVecLen;              // vectors per tile
+    static constexpr int WARPS_M = MS / WM;
+    static constexpr int NCW = QT * WARPS_M;             // warps (all of them compute)
+    static constexpr int NCT = NCW * 32;
+    static constexpr int THREADS = NCT;
+    static constexpr int MT = WM / 8;                    // rows per thread (8, 4 or 2)
+    static constexpr int DQ = (QT > 4) ? QT : 4;         // index ints per compressed row held per stage
+    static constexpr int A_BYTES = KS * MS * 4;
+    static constexpr int B_BYTES = WS * NS * 4;
+    static constexpr int D_BYTES = ((WS * DQ * 4 + 127) / 128) * 128;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + D_BYTES;
+    // Registers allow 512 threads per SM at 128 registers; shared memory is split to match.
+    static constexpr int MIN_BLOCKS = (512 / THREADS) > 4 ? 4 : (512 / THREADS);
+    static constexpr int BUDGET = (224 * 1024) / MIN_BLOCKS - 2048;
+    static constexpr int ST0 = BUDGET / STAGE_BYTES;
+    static constexpr int STAGES = ST0 < 2 ? 2 : (ST0 > 6 ? 6 : ST0);
+    static constexpr int BAR_BYTES = 128;                // 2*STAGES mbarriers + flags
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 128;   // + alignment slack
+    static_assert(MS % WM == 0 && (WM == 64 || WM == 32 || WM == 16), "warp tile");
+    static_assert(2 * STAGES * 8 + 16 <= BAR_BYTES, "barrier block");
+    static_assert(THREADS <= 512, "tile too large");
+};
+
+template <int MS, int NS, int WM, int WS, int MODE>
+__global__ void __launch_bounds__((FfmaCfg<MS, NS, WM, WS, MODE>::THREADS), (FfmaCfg<MS, NS, WM, WS, MODE>::MIN_BLOCKS))
+nm_gemm_ffma_kernel(const GemmArgs g)
+{
+    using Cfg = FfmaCfg<MS, NS, WM, WS, MODE>;
+    constexpr int KS = Cfg::KS, QT = Cfg::QT, NCW = Cfg::NCW, NCT = Cfg::NCT, MT = Cfg::MT, STAGES = Cfg::STAGES;
+
+    extern __shared__ unsigned char smem_raw[];
+    // 128-byte aligned base (dynamic shared memory is only guaranteed 16).
+    unsigned char* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
+    unsigned char* ring = smem;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * STAGES);
+    volatile int* last_flag = abort_flag + 1;
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int bj = blockIdx.x * NS;
+    const int bi = blockIdx.y * MS;
+    const int z = blockIdx.z;
+
+    int win0, nwin;
+    slice_range(g.n_win, g.split_k, z, win0, nwin);
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&bars[s]), 1);              // full: one arrive (with expect_tx) by the filling warp
+            mbar_init(smem_u32(&bars[STAGES + s]), NCW);   // empty: one arrive per warp
+        }
+        *abort_flag = 0;
+        *last_flag = 0;
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    const int rows_here = min(MS, g.M - bi);               // rows of the tile that exist
+    const int cols_here = min(NS, g.N - bj);               // columns of the tile that exist
+    const int layout_ns = g.qs_l * kVecLen;
+    const int lb0 = bj / layout_ns;                        // first packed index block under the tile
+    const int nlb = (bj + cols_here - 1) / layout_ns - lb0 + 1;
+    const int d_chunk = WS * g.qs_l;                       // ints of one block's window
+
+    const int vec = warp % QT, wm = warp / QT;
+    const int lm = (lane & 15) >> 1;
+    const bool live = (vec * kVecLen < cols_here);         // vectors past N idle but keep the ring moving
+
+    // ---- filling one stage: the whole warp calls this (warp-uniform arguments) ----
+    // Window `itl` (relative to the slice) goes to stage itl % STAGES.  c0/c1 are this
+    // lane's two column_info entries of that window (HIGH only).  Returns false if the
+    // bounded wait for the stage's release gave up.
+    const uint32_t a_row_bytes = static_cast<uint32_t>(rows_here) * 4u;
+    const uint32_t b_row_bytes = static_cast<uint32_t>(cols_here) * 4u;
+    const uint32_t d_bytes = static_cast<uint32_t>(d_chunk) * 4u;
+    const int* ci_base = (MODE == kModeHigh) ? g.cinfo + (static_cast<size_t>(lb0) * g.n_win + win0) * KS : nullptr;
+    auto fill = [&](int itl, int c0, int c1) -> bool {
+        const int s = itl % STAGES;
+        const int win = win0 + itl;
+        const uint32_t full = smem_u32(&bars[s]);
+        if (itl >= STAGES) {
+            const bool ok = mbar_wait_bounded(smem_u32(&bars[STAGES + s]), ((itl / STAGES) - 1) & 1, abort_flag);
+            if (!__all_sync(0xffffffffu, ok)) {            // the whole warp gives up together
+                if (lane == 0) atomicMax(g.status, kDevTimeoutEmpty);
+                return false;
+            }
+        }
+        const uint32_t as = smem_u32(ring + s * Cfg::STAGE_BYTES), bs = as + Cfg::A_BYTES, ds = bs + Cfg::B_BYTES;
+        uint32_t tx = WS * b_row_bytes + nlb * d_bytes;
+        if (MODE == kModeLow) {
+            tx += KS * a_row_bytes;
+        } else {
+            const unsigned m0 = __ballot_sync(0xffffffffu, c0 >= 0), m1 = __ballot_sync(0xffffffffu, c1 >= 0);
+            tx += (__popc(m0) + __popc(m1)) * a_row_bytes;
+        }
+        if (lane == 0) mbar_arrive_expect_tx(full, tx);
+        __syncwarp();
+        if (MODE == kModeLow) {
+            const float* src = g.A + (static_cast<size_t>(win) * KS + lane) * g.M + bi;
+            bulk_g2s(as + lane * (MS * 4), src, a_row_bytes, full);
+        } else {
+            const float* src = g.A + static_cast<size_t>(win) * KS * g.M + bi;
+            if (c0 >= 0) bulk_g2s(as + lane * (MS * 4), src + static_cast<size_t>(c0) * g.M, a_row_bytes, full);
+            if (c1 >= 0) bulk_g2s(as + (lane + 32) * (MS * 4), src + static_cast<size_t>(c1) * g.M, a_row_bytes, full);
+        }
+        if (lane < WS) {
+            const float* src = g.B + (static_cast<size_t>(win) * WS + lane) * g.N + bj;
+            bulk_g2s(bs + lane * (NS * 4), src, b_row_bytes, full);
+        }
+        if (lane < nlb) {
+            const int* src = g.D + static_cast<size_t>(lb0 + lane) * g.W * g.qs_l + static_cast<size_t>(win) * d_chunk;
+            bulk_g2s(ds + lane * d_bytes, src, d_bytes, full);
+        }
+        return true;
+    };
+
+    // Prologue: the first STAGES-1 windows, one filling warp each.
+    for (int itl = 0; itl < STAGES - 1 && itl < nwin; ++itl) {
+        if (itl % NCW == warp) {
+            int c0 = -1, c1 = -1;
+            if (MODE == kModeHigh) {
+                c0 = __ldg(ci_base + itl * KS + lane);
+                c1 = __ldg(ci_base + itl * KS + lane + 32);
+            }
+            fill(itl, c0, c1);
+        }
+    }
+
+    float acc[MT][8];
+#pragma unroll
+    for (int i = 0; i < MT; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+
+    const int q = bj / kVecLen + vec;                      // global vector number
+    const int d_off = ((q / g.qs_l - lb0) * d_chunk + q % g.qs_l) * 4;
+    const int d_stride = g.qs_l * 4;
+    const int a_off = (wm * WM + lm * (MT >= 4 ? 4 : 2)) * 4;
+    const int b_off = (vec * kVecLen + (lane >> 4) * 8 + (lane & 1) * 4) * 4;
+
+    // The warps take turns refilling the ring: at the top of iteration `it`, warp
+    // it % NCW loads window it+STAGES-1 into the stage that window it-1 has left, so
+    // STAGES-1 windows are in flight while window `it` is multiplied.  The column_info
+    // entries a fill needs are read one iteration ahead.
+    int c0 = -1, c1 = -1;
+    if (MODE == kModeHigh && warp == 0 && STAGES - 1 < nwin) {
+        c0 = __ldg(ci_base + (STAGES - 1) * KS + lane);
+        c1 = __ldg(ci_base + (STAGES - 1) * KS + lane + 32);
+    }
+    for (int it = 0; it < nwin; ++it) {
+        const int s = it % STAGES;
+        const int nxt = it + STAGES - 1;
+        if (nxt < nwin && it % NCW == warp) {
+            if (!fill(nxt, c0, c1)) break;
+        }
+        if (MODE == kModeHigh && nxt + 1 < nwin && (it + 1) % NCW == warp) {
+            c0 = __ldg(ci_base + (nxt + 1) * KS + lane);
+            c1 = __ldg(ci_base + (nxt + 1) * KS + lane + 32);
+        }
+        const bool ok = mbar_wait_bounded(smem_u32(&bars[s]), (it / STAGES) & 1, abort_flag);
+        if (!__all_sync(0xffffffffu, ok)) {                // the whole warp gives up together
+            if (lane == 0) atomicMax(g.status, kDevTimeoutFull);
+            break;
+        }
+        if (live) {
+            const unsigned char* st = ring + s * Cfg::STAGE_BYTES;
+            const unsigned char* as = st + a_off;
+            const unsigned char* bs = st + Cfg::A_BYTES + b_off;
+            const unsigned char* ds = st + Cfg::A_BYTES + Cfg::B_BYTES + d_off;
+
+            int row_off[WS];
+#pragma unroll
+            for (int p = 0; p < WS; ++p) row_off[p] = *reinterpret_cast<const int*>(ds + p * d_stride) * (MS * 4);
+
+            float a[2][MT], b[2][8];
+            auto load = [&](int p, int buf) {
+                const unsigned char* ap = as + row_off[p];
+                if constexpr (MT == 8) {
+                    *reinterpret_cast<float4*>(&a[buf][0]) = *reinterpret_cast<const float4*>(ap);
+                    *reinterpret_cast<float4*>(&a[buf][4]) = *reinterpret_cast<const float4*>(ap + 32 * 4);
+                } else if constexpr (MT == 4) {
+                    *reinterpret_cast<float4*>(&a[buf][0]) = *reinterpret_cast<const float4*>(ap);
+                } else {
+                    *reinterpret_cast<float2*>(&a[buf][0]) = *reinterpret_cast<const float2*>(ap);
+                }
+                const unsigned char* bp = bs + p * (NS * 4);
+                *reinterpret_cast<float4*>(&b[buf][0]) = *reinterpret_cast<const float4*>(bp);
+                *reinterpret_cast<float4*>(&b[buf][4]) = *reinterpret_cast<const float4*>(bp + 16 * 4);
+            };
+            load(0, 0);
+#pragma unroll
+            for (int p = 0; p < WS; ++p) {
+                if (p + 1 < WS) load(p + 1, (p + 1) & 1);
+#pragma unroll
+                for (int i = 0; i < MT; ++i) {
+#pragma unroll
+                    for (int jj = 0; jj < 8; ++jj) {
+                        const int j = (i & 1) ? 7 - jj : jj;          // serpentine: neighbours share an operand register
+                        acc[i][j] = fmaf(a[p & 1][i], b[p & 1][j], acc[i][j]);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bars[STAGES + s]));
+    }
+
+    // ---------------------------------------------------------------- epilogue
+    const bool aborted = (*abort_flag != 0);
+    const int col0 = bj + vec * kVecLen + (lane >> 4) * 8 + (lane & 1) * 4;      // and col0 + 16
+    const bool store = live && !aborted;
+    auto row_of = [&](int i) {
+        return bi + wm * WM + ((MT == 8) ? ((i < 4) ? lm * 4 + i : 32 + lm * 4 + (i - 4))
+                                         : ((MT == 4) ? lm * 4 + i : lm * 2 + i));
+    };
+
+    if (g.split_k == 1) {
+        if (store) {
+#pragma unroll
+            for (int i = 0; i < MT; ++i) {
+                const int r = row_of(i);
+                if (r < g.M) {
+                    float* cp = g.C + static_cast<size_t>(r) * g.N + col0;
+                    *reinterpret_cast<float4*>(cp) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+                    *reinterpret_cast<float4*>(cp + 16) = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+                }
+            }
+        }
+        return;
+    }
+
+    const size_t tile = static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x;
+    constexpr int E = MT * 2;                              // float4 words per thread
+    float4* part = reinterpret_cast<float4*>(g.partial) + (tile * g.split_k) * (static_cast<size_t>(E) * NCT);
+    if (!aborted) {
+        float4* mine = part + static_cast<size_t>(z) * E * NCT + tid;
+#pragma unroll
+        for (int i = 0; i < MT; ++i) {
+            __stcg(mine + (2 * i) * NCT, make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]));
+            __stcg(mine + (2 * i + 1) * NCT, make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]));
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned prev = atomicAdd(&g.counters[tile], 1u);
+        if (prev == static_cast<unsigned>(g.split_k) - 1u) {
+            *last_flag = 1;
+            g.counters[tile] = 0u;                         // ready for the next call
+        }
+    }
+    __syncthreads();
+    if (*last_flag == 0) return;
+    __threadfence();
+    if (!store) return;
+    float4 sum[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) sum[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < g.split_k; ++s) {                  // fixed order: slice 0, 1, ...
+        const float4* src = part + static_cast<size_t>(s) * E * NCT + tid;
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            const float4 v = __ldcg(src + e * NCT);
+            sum[e].x += v.x; sum[e].y += v.y; sum[e].z += v.z; sum[e].w += v.w;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+        const int r = row_of(i);
+        if (r < g.M) {
+            float* cp = g.C + static_cast<size_t>(r) * g.N + col0;
+            *reinterpret_cast<float4*>(cp) = sum[2 * i];
+            *reinterpret_cast<float4*>(cp + 16) = sum[2 * i + 1];
+        }
+    }
+}
+
+// Host-side launcher of one variant; sets the dynamic shared-memory limit once per device.
+template <int MS, int NS, int WM, int WS, int MODE>
+cudaError_t launch_ffma(const GemmArgs& a, dim3 grid, cudaStream_t st)
+{
+    using Cfg = FfmaCfg<MS, NS, WM, WS, MODE>;
+    auto kernel = nm_gemm_ffma_kernel<MS, NS, WM, WS, MODE>;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 64 && !configured[dev]) {
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    kernel<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(a);
+    return cudaGetLastError();
+}
+
+#define NMSPMM_FFMA_VARIANT(ID, MS, NS, WM, WS, MODE)                                                   \
+    FfmaVariant { ID, MS, NS, WS, MODE, FfmaCfg<MS, NS, WM, WS, MODE>::THREADS,                          \
+                  FfmaCfg<MS, NS, WM, WS, MODE>::SMEM_BYTES, FfmaCfg<MS, NS, WM, WS, MODE>::STAGES,      \
+                  FfmaCfg<MS, NS, WM, WS, MODE>::MIN_BLOCKS, &launch_ffma<MS, NS, WM, WS, MODE> }
+
+// All tiles for one (WS, MODE).
+#define NMSPMM_FFMA_TILES(WS, MODE)                          \
+    NMSPMM_FFMA_VARIANT(kTile128x128, 128, 128, 64, WS, MODE), \
+    NMSPMM_FFMA_VARIANT(kTile64x128, 64, 128, 64, WS, MODE),   \
+    NMSPMM_FFMA_VARIANT(kTile32x128, 32, 128, 32, WS, MODE),   \
+    NMSPMM_FFMA_VARIANT(kTile16x128, 16, 128, 16, WS, MODE),   \
+    NMSPMM_FFMA_VARIANT(kTile128x64, 128, 64, 64, WS, MODE),   \
+    NMSPMM_FFMA_VARIANT(kTile128x32, 128, 32, 64, WS, MODE)
+
+}  // namespace nmspmm

@@ -1,0 +1,27 @@
+// Internal host-side declarations shared by the library's translation units.
+#pragma once
+#include <cuda_runtime.h>
+#include "gemm_args.h"
+
+namespace nmspmm {
+
+cudaError_t launch_trans_index(int* DT, int W, int Q, int pruning_N, int pruning_M, cudaStream_t st);
+cudaError_t launch_retile(const int* DT, int* D, int W, int Q, int Qs, cudaStream_t st);
+cudaError_t launch_preprocess_high(const int* DT, int* D, int* cinfo, int pm, int pn, int W, int Q, int Qs,
+                                   int fuse, int tail_ints, cudaStream_t st);
+
+// One compiled FFMA kernel variant.
+struct FfmaVariant {
+    int tile_id;        // nmspmm_tile
+    int ms, ns;         // CTA tile
+    int ws;             // compressed rows per window
+    int mode;           // kModeLow / kModeHigh
+    int threads, smem_bytes, stages, min_blocks;
+    cudaError_t (*launch)(const GemmArgs&, dim3 grid, cudaStream_t st);
+};
+// Returns nullptr when the combination was not compiled.
+const FfmaVariant* find_ffma_variant(int tile_id, int ws, int mode);
+
+cudaError_t measure_ffma_peak(double* tflops, cudaStream_t st);
+
+}  // namespace nmspmm

@@ -1,0 +1,115 @@
+"""CPU-side checks of the boundary: the library loads and exports every symbol the
+header declares, argument validation and plan selection behave, and the drop-in C++
+names exist with the reference's mangling.  No kernel is launched."""
+import ctypes
+import os
+import re
+import subprocess
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol(pkg):
+    header = open(os.path.join(ROOT, "include", "nmspmm_b200.h")).read()
+    declared = set(re.findall(r"\b(nmspmm_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    lib = ctypes.CDLL(pkg.LIB_PATH)
+    for name in sorted(declared):
+        assert hasattr(lib, name), f"{name} declared in include/nmspmm_b200.h but not exported"
+    assert declared == set(pkg.C_ABI_SYMBOLS)
+
+
+def test_dropin_cpp_symbols_have_reference_mangling(pkg):
+    """The reference's header declares C++ free functions (one takes int&), so the
+    drop-in must export the same mangled names."""
+    out = subprocess.run(["nm", "-D", "--defined-only", pkg.LIB_PATH], capture_output=True, text=True).stdout
+    names = set(line.split()[-1] for line in out.splitlines() if line.strip())
+    want = ["_Z26PreProcessing_low_sparsityPiiii", "_Z27PreProcessing_high_sparsityPiiiS_iiii", "_Z10transIndexPiiiiRiS0_"]
+    for size in ("huge", "large", "medium", "small"):
+        want.append(f"_Z{len('nmGEMM_' + size + '_matrices_low_sparsity')}nmGEMM_{size}_matrices_low_sparsityPfS_PiS_iiiifi")
+        want.append(f"_Z{len('nmGEMM_' + size + '_matrices_high_sparsity')}nmGEMM_{size}_matrices_high_sparsityPfS_PiS0_S_iiiifi")
+    for w in want:
+        assert w in names, w
+
+
+def test_status_strings(pkg):
+    lib = pkg.load_library()
+    assert lib.nmspmm_status_string(0) == b"ok"
+    assert b"unsupported" in lib.nmspmm_status_string(pkg.UNSUPPORTED)
+    assert lib.nmspmm_version() >= 0x000100
+
+
+@pytest.mark.parametrize("M,N,K,n_keep,fmt,Ns,expect_tile", [
+    (4096, 4096, 4096, 16, 0, 128, (128, 128)),
+    (4096, 4096, 4096, 8, 1, 128, (128, 128)),
+    (16, 11008, 4096, 8, 1, 128, (16, 128)),
+    (64, 11008, 4096, 8, 1, 128, (64, 128)),
+    (256, 11008, 4096, 8, 1, 128, (128, 128)),
+    (192, 1024, 1024, 16, 0, 64, (64, 128)),
+    (4096, 4096, 4096, 4, 1, 64, (128, 64)),
+    (4096, 4096, 4096, 4, 1, 32, (128, 32)),
+])
+def test_plan_selection(pkg, M, N, K, n_keep, fmt, Ns, expect_tile):
+    info = pkg.plan(pkg.make_desc(M, N, K, n_keep, fmt, Ns))
+    assert (info.tile_m, info.tile_n) == expect_tile
+    assert info.grid_x == -(-N // info.tile_n) and info.grid_y == -(-M // info.tile_m)
+    ws = n_keep if fmt == 0 else 2 * n_keep
+    n_win = K // 32 * n_keep // ws
+    assert 1 <= info.split_k <= n_win and info.grid_z == info.split_k
+    assert info.stages >= 2 and info.smem_bytes <= 227 * 1024
+    d = pkg.make_desc(M, N, K, n_keep, fmt, Ns)
+    need = pkg.workspace_bytes(d)
+    if info.split_k == 1:
+        assert need == 0
+    else:
+        tiles = info.grid_x * info.grid_y
+        assert need >= tiles * info.split_k * info.tile_m * info.tile_n * 4
+
+
+def test_split_k_fills_the_machine_for_skinny_shapes(pkg):
+    big = pkg.plan(pkg.make_desc(4096, 4096, 4096, 8, 1, 128))
+    assert big.split_k == 1
+    skinny = pkg.plan(pkg.make_desc(16, 11008, 4096, 8, 1, 128))
+    assert skinny.split_k > 1
+    deep = pkg.plan(pkg.make_desc(128, 1024, 131072, 4, 1, 128))
+    assert deep.split_k >= 16
+    forced = pkg.plan(pkg.make_desc(128, 1024, 131072, 4, 1, 128, split_k=7))
+    assert forced.split_k == 7
+    clamped = pkg.plan(pkg.make_desc(128, 128, 64, 16, 0, 128, split_k=9))
+    assert clamped.split_k == 2            # only two windows exist
+
+
+@pytest.mark.parametrize("kw,status", [
+    (dict(M=0), 1), (dict(N=100), 1), (dict(K=48), 1), (dict(M=6), 1), (dict(layout_ns=96), 1),
+    (dict(n_keep=10), 2), (dict(n_keep=16, fmt=1), 2), (dict(n_keep=4, fmt=0), 2), (dict(path=1), 2),
+    (dict(N=192, layout_ns=128), 1), (dict(K=96, n_keep=8, fmt=1), 1), (dict(split_k=-1), 1),
+])
+def test_bad_descriptions_are_rejected(pkg, kw, status):
+    base = dict(M=128, N=256, K=256, n_keep=16, fmt=0, layout_ns=128, path=0, split_k=0)
+    base.update(kw)
+    d = pkg.make_desc(base["M"], base["N"], base["K"], base["n_keep"], base["fmt"], base["layout_ns"],
+                      base["path"], base["split_k"])
+    info = pkg.PlanInfo()
+    rc = pkg.load_library().nmspmm_gemm_plan(ctypes.byref(d), ctypes.byref(info))
+    assert rc == status, (kw, rc)
+
+
+def test_sparsity_argument_mapping(pkg):
+    assert [pkg.n_keep_of(s) for s in (0.0, 0.5, 0.625, 0.75, 0.875)] == [32, 16, 12, 8, 4]
+    assert [pkg.format_of(n) for n in (32, 16, 12, 8, 4)] == [0, 0, 0, 1, 1]
+    with pytest.raises(ValueError):
+        pkg.n_keep_of(0.3)
+
+
+def test_partition_columns(pkg_host):
+    sh = pkg_host.sharding
+    assert sh.partition_columns(28672, 8, 128) == [(i * 3584, (i + 1) * 3584) for i in range(8)]
+    parts = sh.partition_columns(11008, 4, 128)          # 86 blocks over 4 ranks: 22, 22, 21, 21
+    assert [c1 - c0 for c0, c1 in parts] == [2816, 2816, 2688, 2688]
+    assert parts[0][0] == 0 and parts[-1][1] == 11008 and all(a[1] == b[0] for a, b in zip(parts, parts[1:]))
+    with pytest.raises(ValueError):
+        sh.partition_columns(256, 4, 128)
+    with pytest.raises(ValueError):
+        sh.partition_columns(200, 1, 128)
