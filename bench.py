@@ -248,20 +248,21 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
     # This rank's column shard: 4096 columns of B (its own seed), A shared by all ranks.
     M, K, n_local = M_SQ, K_SQ, N_SQ
-    p = pkg.formats.make_random(M, n_local, K, HEADLINE_KEEP, seed=0)
+    keep = args.n_keep if args.kernel_only else HEADLINE_KEEP
+    p = pkg.formats.make_random(M, n_local, K, keep, seed=0)
     if rank != 0:
-        q = pkg.formats.make_random(4, n_local, K, HEADLINE_KEEP, seed=1000 + rank)
+        q = pkg.formats.make_random(4, n_local, K, keep, seed=1000 + rank)
         p.BT, p.DT = q.BT, q.DT
     op = pkg.NMSpMM.from_problem(p, layout_ns=128)
     A_sets = [torch.from_numpy(p.A_km).cuda()]
     for s in range(1, SETS):
         A_sets.append(torch.roll(A_sets[0], s * 131, dims=1).contiguous())
     C_sets = [torch.empty((M, n_local), dtype=torch.float32, device="cuda") for _ in range(SETS)]
-    desc = op.desc(M)
+    desc = op.desc(M, tile=args.tile, split_k=args.split_k)
     plan = pkg.plan(desc)
 
     def step(i):
-        op.matmul(A_sets[i % SETS], out=C_sets[i % SETS])
+        op.matmul(A_sets[i % SETS], out=C_sets[i % SETS], tile=args.tile, split_k=args.split_k)
 
     for i in range(max(3, args.warmup)):
         step(i)
@@ -277,6 +278,14 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     ms_per_step = ms / args.steps
     useful = 2.0 * M * n_local * p.W
     value = world * useful / (ms_per_step * 1e-3) / 1e12
+    if args.kernel_only:
+        if rank == 0:
+            print(json.dumps({"kernel_only": True, "n_keep": keep, "ms_per_step": ms_per_step, "useful_tflops": value,
+                              "tile": [plan.tile_m, plan.tile_n], "split_k": plan.split_k, "stages": plan.stages,
+                              "clocks": sampler.summary()}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---- roofline of the dominant (only) kernel, per GPU --------------------------
     peaks = {}
@@ -368,6 +377,11 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="only the resident-operand steps (profiling runs): no e2e, CPU baseline or ratio sweep")
+    ap.add_argument("--n-keep", type=int, default=HEADLINE_KEEP, help="kept rows per 32-window for --kernel-only runs")
+    ap.add_argument("--tile", type=int, default=0, help="force a CTA tile id (tuning runs)")
+    ap.add_argument("--split-k", type=int, default=0, help="force the number of K slices (tuning runs)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

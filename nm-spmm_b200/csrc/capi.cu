@@ -104,15 +104,17 @@ static int check_desc(const nmspmm_gemm_desc* d, int* ws_out, int* mode_out)
     return NMSPMM_OK;
 }
 
-static int pick_tile(const nmspmm_gemm_desc* d, int mode)
+static int pick_tile(const nmspmm_gemm_desc* d, int sms)
 {
-    if (mode == kModeHigh && d->layout_ns == 64) return kTile128x64;    // a tile must sit inside one index block
-    if (mode == kModeHigh && d->layout_ns == 32) return kTile128x32;
     if (d->M <= 16) return kTile16x128;
     if (d->M <= 32) return kTile32x128;
     if (d->M <= 64) return kTile64x128;
     const int pad128 = (d->M + 127) / 128 * 128, pad64 = (d->M + 63) / 64 * 64;
-    return (pad64 < pad128) ? kTile64x128 : kTile128x128;
+    if (pad64 < pad128) return kTile64x128;
+    // The widest tile reads the A window once for eight vectors; use it when it still
+    // gives every SM at least two tiles.
+    const long long wide = static_cast<long long>((d->M + 127) / 128) * ((d->N + 255) / 256);
+    return (wide >= 2LL * sms) ? kTile128x256 : kTile128x128;
 }
 
 static int make_plan(const nmspmm_gemm_desc* d, int sms, Plan* p)
@@ -121,10 +123,9 @@ static int make_plan(const nmspmm_gemm_desc* d, int sms, Plan* p)
     int rc = check_desc(d, &ws, &mode);
     if (rc != NMSPMM_OK) return rc;
     if (d->path != NMSPMM_PATH_FP32) return NMSPMM_UNSUPPORTED;
-    const int tile = d->tile ? d->tile : pick_tile(d, mode);
+    const int tile = d->tile ? d->tile : pick_tile(d, sms > 0 ? sms : 148);
     const FfmaVariant* v = find_ffma_variant(tile, ws, mode);
     if (!v) return NMSPMM_UNSUPPORTED;
-    if (mode == kModeHigh && (d->layout_ns % v->ns) != 0) return NMSPMM_UNSUPPORTED;
     p->v = v;
     p->ws = ws;
     p->W = d->K / 32 * d->n_keep;

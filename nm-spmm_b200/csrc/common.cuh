@@ -1,5 +1,5 @@
-// Device-side building blocks shared by the sm_100a kernels: mbarrier, bulk
-// asynchronous copies (the TMA engine's untiled form) and bounded waits.
+// Device-side building blocks shared by the sm_100a kernels: mbarrier, TMA copies
+// (tiled tensor form and untiled bulk form) and bounded waits.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -89,25 +89,14 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src_gmem
         : "memory");
 }
 
-__device__ __forceinline__ float4 lds128(uint32_t addr)
+// Tiled 2-D tensor copy global -> shared through a tensor map ({x, y} = element
+// coordinates of the box corner, x innermost and a multiple of 4 floats).
+__device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void* tensor_map, int x, int y, uint32_t bar)
 {
-    float4 v;
-    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
-    return v;
-}
-
-__device__ __forceinline__ float2 lds64(uint32_t addr)
-{
-    float2 v;
-    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
-    return v;
-}
-
-__device__ __forceinline__ int lds32i(uint32_t addr)
-{
-    int v;
-    asm volatile("ld.shared.s32 %0, [%1];" : "=r"(v) : "r"(addr));
-    return v;
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tensor_map)), "r"(bar), "r"(x), "r"(y)
+        : "memory");
 }
 
 // Which windows (of n_win) slice z of split_k owns: the first n_win % split_k

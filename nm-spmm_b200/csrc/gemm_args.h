@@ -13,8 +13,7 @@ enum nmspmm_tile {
     kTile64x128 = 2,
     kTile32x128 = 3,
     kTile16x128 = 4,
-    kTile128x64 = 5,
-    kTile128x32 = 6,
+    kTile128x256 = 5,
     kTileCount
 };
 

@@ -2,25 +2,30 @@
 //
 // One CTA computes an MS x NS tile of C over a contiguous range of k windows
 // (its split-K slice).  Each window's operands are streamed into a STAGES-deep
-// shared-memory ring with bulk asynchronous copies (the TMA engine), completion
-// counted on mbarriers; the warps take turns issuing a window's copies (a few
-// instructions per warp every NCW windows) and otherwise only compute: there is
-// no CTA-wide barrier in the main loop.  Per window the ring holds
-//     As  [KS][MS]   LOW : the dense 32-k window of A (A is col-major, so k-row r is
-//                          MS contiguous floats)
-//                    HIGH: only the rows listed in column_info for this (Ns block,
-//                          64-k window) -- row r holds A column column_info[r]
+// shared-memory ring by the TMA engine, completion counted on mbarriers: one tiled
+// tensor copy for the window of A, one for the window of B, and small bulk copies
+// for the indices.  The warps take turns issuing a window's copies (a few
+// instructions by one warp per window) and otherwise only compute: there is no
+// CTA-wide barrier in the main loop.  Per window the ring holds
+//     As  [KS][MS]   the dense k window of A (A is col-major, so k-row r is MS
+//                    contiguous floats): 32 rows (LOW) or 64 rows (HIGH)
 //     Bs  [WS][NS]   the window's compressed rows of B
 //     Ds  [..]       the window's packed indices for the vectors of the tile
+//     Cs  [..][64]   HIGH only: the window's column_info lists of the index blocks
+//                    under the tile; a packed index is a rank into its block's list
 // and the gather of the reference (src/kernel_64x128_8x8.cu:139-159) stays what it
-// was: the shared-memory row address As[D[p]].  Every consumer warp owns one
-// 32-column vector, so that row is warp-uniform, and the 8x8 register tile reads
-// two 128-bit words of A and two of B per 64 FFMAs.
+// was: the shared-memory row address As[k(p)].  Every warp owns one 32-column
+// vector, so that row is warp-uniform, and the 8x8 register tile reads two 128-bit
+// words of A and two of B per 64 FFMAs.  Unlike the reference's high-sparsity
+// kernels the A window is staged dense (one TMA box instead of one copy per used
+// column), which frees the CTA tile from the packed index block size.
 //
 // split_k > 1: each slice writes its partial tile to scratch; the last slice to
 // arrive (per-tile counter) adds the partials in slice order and writes C, so the
 // result does not depend on arrival order.
 #pragma once
+#include <cuda.h>
+
 #include "common.cuh"
 #include "gemm_args.h"
 #include "kernels.h"
@@ -40,7 +45,9 @@ struct FfmaCfg {
     static constexpr int A_BYTES = KS * MS * 4;
     static constexpr int B_BYTES = WS * NS * 4;
     static constexpr int D_BYTES = ((WS * DQ * 4 + 127) / 128) * 128;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + D_BYTES;
+    static constexpr int CI_BYTES = (MODE == kModeHigh) ? QT * 64 * 4 : 0;   // one list per index block under the tile
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + D_BYTES + CI_BYTES;
+    static constexpr int TX_FIXED = A_BYTES + B_BYTES;   // bytes the two tensor copies always deliver
     // Registers allow 512 threads per SM at 128 registers; shared memory is split to match.
     static constexpr int MIN_BLOCKS = (512 / THREADS) > 4 ? 4 : (512 / THREADS);
     static constexpr int BUDGET = (224 * 1024) / MIN_BLOCKS - 2048;
@@ -55,7 +62,7 @@ struct FfmaCfg {
 
 template <int MS, int NS, int WM, int WS, int MODE>
 __global__ void __launch_bounds__((FfmaCfg<MS, NS, WM, WS, MODE>::THREADS), (FfmaCfg<MS, NS, WM, WS, MODE>::MIN_BLOCKS))
-nm_gemm_ffma_kernel(const GemmArgs g)
+nm_gemm_ffma_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b)
 {
     using Cfg = FfmaCfg<MS, NS, WM, WS, MODE>;
     constexpr int KS = Cfg::KS, QT = Cfg::QT, NCW = Cfg::NCW, NCT = Cfg::NCT, MT = Cfg::MT, STAGES = Cfg::STAGES;
@@ -88,7 +95,6 @@ nm_gemm_ffma_kernel(const GemmArgs g)
     }
     __syncthreads();
 
-    const int rows_here = min(MS, g.M - bi);               // rows of the tile that exist
     const int cols_here = min(NS, g.N - bj);               // columns of the tile that exist
     const int layout_ns = g.qs_l * kVecLen;
     const int lb0 = bj / layout_ns;                        // first packed index block under the tile
@@ -100,14 +106,11 @@ nm_gemm_ffma_kernel(const GemmArgs g)
     const bool live = (vec * kVecLen < cols_here);         // vectors past N idle but keep the ring moving
 
     // ---- filling one stage: the whole warp calls this (warp-uniform arguments) ----
-    // Window `itl` (relative to the slice) goes to stage itl % STAGES.  c0/c1 are this
-    // lane's two column_info entries of that window (HIGH only).  Returns false if the
-    // bounded wait for the stage's release gave up.
-    const uint32_t a_row_bytes = static_cast<uint32_t>(rows_here) * 4u;
-    const uint32_t b_row_bytes = static_cast<uint32_t>(cols_here) * 4u;
+    // Window `itl` (relative to the slice) goes to stage itl % STAGES.  Returns false if
+    // the bounded wait for the stage's release gave up.
     const uint32_t d_bytes = static_cast<uint32_t>(d_chunk) * 4u;
-    const int* ci_base = (MODE == kModeHigh) ? g.cinfo + (static_cast<size_t>(lb0) * g.n_win + win0) * KS : nullptr;
-    auto fill = [&](int itl, int c0, int c1) -> bool {
+    const uint32_t tx_bytes = Cfg::TX_FIXED + nlb * (d_bytes + (MODE == kModeHigh ? 256u : 0u));
+    auto fill = [&](int itl) -> bool {
         const int s = itl % STAGES;
         const int win = win0 + itl;
         const uint32_t full = smem_u32(&bars[s]);
@@ -119,44 +122,26 @@ nm_gemm_ffma_kernel(const GemmArgs g)
             }
         }
         const uint32_t as = smem_u32(ring + s * Cfg::STAGE_BYTES), bs = as + Cfg::A_BYTES, ds = bs + Cfg::B_BYTES;
-        uint32_t tx = WS * b_row_bytes + nlb * d_bytes;
-        if (MODE == kModeLow) {
-            tx += KS * a_row_bytes;
-        } else {
-            const unsigned m0 = __ballot_sync(0xffffffffu, c0 >= 0), m1 = __ballot_sync(0xffffffffu, c1 >= 0);
-            tx += (__popc(m0) + __popc(m1)) * a_row_bytes;
+        if (lane == 0) {
+            mbar_arrive_expect_tx(full, tx_bytes);
+            tma_load_2d(as, &map_a, bi, win * KS, full);      // rows/columns past the tensor arrive as zeros
+            tma_load_2d(bs, &map_b, bj, win * WS, full);
         }
-        if (lane == 0) mbar_arrive_expect_tx(full, tx);
         __syncwarp();
-        if (MODE == kModeLow) {
-            const float* src = g.A + (static_cast<size_t>(win) * KS + lane) * g.M + bi;
-            bulk_g2s(as + lane * (MS * 4), src, a_row_bytes, full);
-        } else {
-            const float* src = g.A + static_cast<size_t>(win) * KS * g.M + bi;
-            if (c0 >= 0) bulk_g2s(as + lane * (MS * 4), src + static_cast<size_t>(c0) * g.M, a_row_bytes, full);
-            if (c1 >= 0) bulk_g2s(as + (lane + 32) * (MS * 4), src + static_cast<size_t>(c1) * g.M, a_row_bytes, full);
-        }
-        if (lane < WS) {
-            const float* src = g.B + (static_cast<size_t>(win) * WS + lane) * g.N + bj;
-            bulk_g2s(bs + lane * (NS * 4), src, b_row_bytes, full);
-        }
         if (lane < nlb) {
             const int* src = g.D + static_cast<size_t>(lb0 + lane) * g.W * g.qs_l + static_cast<size_t>(win) * d_chunk;
             bulk_g2s(ds + lane * d_bytes, src, d_bytes, full);
+            if (MODE == kModeHigh) {
+                const int* ci = g.cinfo + (static_cast<size_t>(lb0 + lane) * g.n_win + win) * 64;
+                bulk_g2s(ds + Cfg::D_BYTES + lane * 256, ci, 256, full);
+            }
         }
         return true;
     };
 
     // Prologue: the first STAGES-1 windows, one filling warp each.
     for (int itl = 0; itl < STAGES - 1 && itl < nwin; ++itl) {
-        if (itl % NCW == warp) {
-            int c0 = -1, c1 = -1;
-            if (MODE == kModeHigh) {
-                c0 = __ldg(ci_base + itl * KS + lane);
-                c1 = __ldg(ci_base + itl * KS + lane + 32);
-            }
-            fill(itl, c0, c1);
-        }
+        if (itl % NCW == warp) fill(itl);
     }
 
     float acc[MT][8];
@@ -166,29 +151,20 @@ nm_gemm_ffma_kernel(const GemmArgs g)
         for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
 
     const int q = bj / kVecLen + vec;                      // global vector number
-    const int d_off = ((q / g.qs_l - lb0) * d_chunk + q % g.qs_l) * 4;
+    const int lb = q / g.qs_l - lb0;                       // index block of this vector, relative to the tile
+    const int d_off = (lb * d_chunk + q % g.qs_l) * 4;
     const int d_stride = g.qs_l * 4;
     const int a_off = (wm * WM + lm * (MT >= 4 ? 4 : 2)) * 4;
     const int b_off = (vec * kVecLen + (lane >> 4) * 8 + (lane & 1) * 4) * 4;
 
     // The warps take turns refilling the ring: at the top of iteration `it`, warp
     // it % NCW loads window it+STAGES-1 into the stage that window it-1 has left, so
-    // STAGES-1 windows are in flight while window `it` is multiplied.  The column_info
-    // entries a fill needs are read one iteration ahead.
-    int c0 = -1, c1 = -1;
-    if (MODE == kModeHigh && warp == 0 && STAGES - 1 < nwin) {
-        c0 = __ldg(ci_base + (STAGES - 1) * KS + lane);
-        c1 = __ldg(ci_base + (STAGES - 1) * KS + lane + 32);
-    }
+    // STAGES-1 windows are in flight while window `it` is multiplied.
     for (int it = 0; it < nwin; ++it) {
         const int s = it % STAGES;
         const int nxt = it + STAGES - 1;
         if (nxt < nwin && it % NCW == warp) {
-            if (!fill(nxt, c0, c1)) break;
-        }
-        if (MODE == kModeHigh && nxt + 1 < nwin && (it + 1) % NCW == warp) {
-            c0 = __ldg(ci_base + (nxt + 1) * KS + lane);
-            c1 = __ldg(ci_base + (nxt + 1) * KS + lane + 32);
+            if (!fill(nxt)) break;
         }
         const bool ok = mbar_wait_bounded(smem_u32(&bars[s]), (it / STAGES) & 1, abort_flag);
         if (!__all_sync(0xffffffffu, ok)) {                // the whole warp gives up together
@@ -203,7 +179,14 @@ nm_gemm_ffma_kernel(const GemmArgs g)
 
             int row_off[WS];
 #pragma unroll
-            for (int p = 0; p < WS; ++p) row_off[p] = *reinterpret_cast<const int*>(ds + p * d_stride) * (MS * 4);
+            for (int p = 0; p < WS; ++p) row_off[p] = *reinterpret_cast<const int*>(ds + p * d_stride);
+            if constexpr (MODE == kModeHigh) {             // rank -> local column through the block's list
+                const int* list = reinterpret_cast<const int*>(st + Cfg::A_BYTES + Cfg::B_BYTES + Cfg::D_BYTES) + lb * 64;
+#pragma unroll
+                for (int p = 0; p < WS; ++p) row_off[p] = list[row_off[p]];
+            }
+#pragma unroll
+            for (int p = 0; p < WS; ++p) row_off[p] *= (MS * 4);
 
             float a[2][MT], b[2][8];
             auto load = [&](int p, int buf) {
@@ -308,7 +291,9 @@ nm_gemm_ffma_kernel(const GemmArgs g)
     }
 }
 
-// Host-side launcher of one variant; sets the dynamic shared-memory limit once per device.
+// Host-side launcher of one variant: encodes the two tensor maps (A as [K][M] with an
+// MS x KS box, B as [W][N] with an NS x WS box) and sets the dynamic shared-memory
+// limit once per device.
 template <int MS, int NS, int WM, int WS, int MODE>
 cudaError_t launch_ffma(const GemmArgs& a, dim3 grid, cudaStream_t st)
 {
@@ -323,7 +308,12 @@ cudaError_t launch_ffma(const GemmArgs& a, dim3 grid, cudaStream_t st)
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
-    kernel<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(a);
+    CUtensorMap map_a, map_b;
+    e = encode_tensor_map_2d(&map_a, a.A, a.M, a.n_win * Cfg::KS, MS, Cfg::KS);
+    if (e != cudaSuccess) return e;
+    e = encode_tensor_map_2d(&map_b, a.B, a.N, a.W, NS, WS);
+    if (e != cudaSuccess) return e;
+    kernel<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(a, map_a, map_b);
     return cudaGetLastError();
 }
 
@@ -338,7 +328,6 @@ cudaError_t launch_ffma(const GemmArgs& a, dim3 grid, cudaStream_t st)
     NMSPMM_FFMA_VARIANT(kTile64x128, 64, 128, 64, WS, MODE),   \
     NMSPMM_FFMA_VARIANT(kTile32x128, 32, 128, 32, WS, MODE),   \
     NMSPMM_FFMA_VARIANT(kTile16x128, 16, 128, 16, WS, MODE),   \
-    NMSPMM_FFMA_VARIANT(kTile128x64, 128, 64, 64, WS, MODE),   \
-    NMSPMM_FFMA_VARIANT(kTile128x32, 128, 32, 64, WS, MODE)
+    NMSPMM_FFMA_VARIANT(kTile128x256, 128, 256, 64, WS, MODE)
 
 }  // namespace nmspmm

@@ -1,5 +1,6 @@
 // Internal host-side declarations shared by the library's translation units.
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include "gemm_args.h"
 
@@ -21,6 +22,10 @@ struct FfmaVariant {
 };
 // Returns nullptr when the combination was not compiled.
 const FfmaVariant* find_ffma_variant(int tile_id, int ws, int mode);
+
+// Row-major 2-D float tensor [rows][cols] (cols innermost) with a box_cols x box_rows box, no swizzle;
+// elements outside the tensor are delivered as zeros.
+cudaError_t encode_tensor_map_2d(CUtensorMap* map, const float* base, int cols, int rows, int box_cols, int box_rows);
 
 cudaError_t measure_ffma_peak(double* tflops, cudaStream_t st);
 

@@ -46,13 +46,14 @@ def test_every_ratio_layout_and_row_count(pkg, orc, n_keep, Ns, M):
     assert rel_err(run(pkg, p, layout_ns=Ns), want) <= FP32_TOL
 
 
-@pytest.mark.parametrize("tile", [1, 2, 3, 4, 5, 6])
+@pytest.mark.parametrize("tile", [1, 2, 3, 4, 5])
 @pytest.mark.parametrize("n_keep,fmt", [(16, 0), (12, 0), (32, 0), (8, 0), (8, 1), (4, 1)])
-def test_every_compiled_tile(pkg, orc, tile, n_keep, fmt):
-    ns = {5: 64, 6: 32}.get(tile, 128)
-    p = pkg.formats.make_random(200, 512, 256, n_keep, seed=40 + tile)      # ragged rows: 200 = 128 + 72
+@pytest.mark.parametrize("layout", [32, 64, 128])
+def test_every_compiled_tile(pkg, orc, tile, n_keep, fmt, layout):
+    """Every tile x ratio x index layout, on a shape with ragged rows (200 = 128 + 72)
+    and a ragged last column tile (640 = 2*256 + 128)."""
+    p = pkg.formats.make_random(200, 640, 256, n_keep, seed=40 + tile)
     want = orc.nm_gemm_f32(p.A_km, p.B_col, p.D_col)
-    layout = ns if fmt == 1 else 64
     assert rel_err(run(pkg, p, layout_ns=layout, fmt=fmt, tile=tile), want) <= FP32_TOL
 
 

@@ -42,14 +42,15 @@ def test_status_strings(pkg):
 
 
 @pytest.mark.parametrize("M,N,K,n_keep,fmt,Ns,expect_tile", [
-    (4096, 4096, 4096, 16, 0, 128, (128, 128)),
-    (4096, 4096, 4096, 8, 1, 128, (128, 128)),
+    (4096, 4096, 4096, 16, 0, 128, (128, 256)),
+    (4096, 4096, 4096, 8, 1, 128, (128, 256)),
+    (1024, 1024, 4096, 8, 1, 128, (128, 128)),
     (16, 11008, 4096, 8, 1, 128, (16, 128)),
     (64, 11008, 4096, 8, 1, 128, (64, 128)),
     (256, 11008, 4096, 8, 1, 128, (128, 128)),
     (192, 1024, 1024, 16, 0, 64, (64, 128)),
-    (4096, 4096, 4096, 4, 1, 64, (128, 64)),
-    (4096, 4096, 4096, 4, 1, 32, (128, 32)),
+    (4096, 4096, 4096, 4, 1, 64, (128, 256)),
+    (8192, 28672, 8192, 8, 1, 32, (128, 256)),
 ])
 def test_plan_selection(pkg, M, N, K, n_keep, fmt, Ns, expect_tile):
     info = pkg.plan(pkg.make_desc(M, N, K, n_keep, fmt, Ns))
