@@ -153,9 +153,11 @@ int nmspmm_gemm_host(const nmspmm_gemm_desc* desc,
 /* Frees the arena of nmspmm_gemm_host and the wrappers' cached scratch. */
 int nmspmm_release_cached(void);
 
-/* Sustained FFMA rate of this GPU in TFLOP/s (2 flops per FFMA), measured with a
- * register-only kernel on `stream` (synchronous).  The FP32 roofline denominator. */
-int nmspmm_measure_ffma_peak(double* tflops_out, void* stream);
+/* Sustained FP32 FMA rate of this GPU in TFLOP/s (2 flops per FMA), measured with a
+ * register-only kernel on `stream` (synchronous; allocates 4 bytes).  packed = 0 uses
+ * scalar FFMA, packed = 1 the two-lane packed FMA of sm_100.  The FP32 roofline
+ * denominator is the larger of the two. */
+int nmspmm_measure_ffma_peak(double* tflops_out, int packed, void* stream);
 
 #ifdef __cplusplus
 }

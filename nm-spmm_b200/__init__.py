@@ -87,7 +87,7 @@ def load_library():
     lib.nmspmm_device_status.argtypes = [ctypes.POINTER(ci), ci]
     lib.nmspmm_gemm_plan.argtypes = [ctypes.POINTER(GemmDesc), ctypes.POINTER(PlanInfo)]
     lib.nmspmm_gemm_host.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp]
-    lib.nmspmm_measure_ffma_peak.argtypes = [ctypes.POINTER(ctypes.c_double), vp]
+    lib.nmspmm_measure_ffma_peak.argtypes = [ctypes.POINTER(ctypes.c_double), ci, vp]
     _lib = lib
     return lib
 
@@ -289,10 +289,12 @@ def gemm_host(desc: GemmDesc, A_km, BT, DT, C, on_current_stream: bool = False) 
     _check("nmspmm_gemm_host", lib.nmspmm_gemm_host(ctypes.byref(desc), ptr(A_km), ptr(BT), ptr(DT), ptr(C), st))
 
 
-def measure_ffma_peak() -> float:
-    """Sustained FP32 FFMA rate of the current GPU in TFLOP/s (register-only kernel)."""
+def measure_ffma_peak(packed: bool = False) -> float:
+    """Sustained FP32 FMA rate of the current GPU in TFLOP/s (register-only kernel);
+    ``packed`` selects the two-lane packed FMA of sm_100 instead of scalar FFMA."""
     out = ctypes.c_double(0.0)
-    _check("nmspmm_measure_ffma_peak", load_library().nmspmm_measure_ffma_peak(ctypes.byref(out), _stream_ptr()))
+    _check("nmspmm_measure_ffma_peak",
+           load_library().nmspmm_measure_ffma_peak(ctypes.byref(out), 1 if packed else 0, _stream_ptr()))
     return out.value
 
 

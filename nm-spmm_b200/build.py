@@ -13,7 +13,7 @@ OBJ = os.path.join(CSRC, "build")
 LIB = os.path.join(HERE, "libnmspmm_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-         "-Xcompiler", "-fPIC", "-I" + os.path.join(ROOT, "include"), "-I" + CSRC]
+         "-Xcompiler", "-fPIC", "-I" + os.path.join(ROOT, "include"), "-I" + CSRC] + os.environ.get("NMSPMM_NVCC_EXTRA", "").split()
 
 
 def _sources():

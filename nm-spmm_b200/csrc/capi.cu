@@ -506,10 +506,10 @@ int nmspmm_release_cached(void)
     return NMSPMM_OK;
 }
 
-int nmspmm_measure_ffma_peak(double* tflops_out, void* stream)
+int nmspmm_measure_ffma_peak(double* tflops_out, int packed, void* stream)
 {
     if (!tflops_out) return NMSPMM_INVALID_ARGUMENT;
-    cudaError_t e = measure_ffma_peak(tflops_out, static_cast<cudaStream_t>(stream));
+    cudaError_t e = measure_ffma_peak(tflops_out, packed ? 1 : 0, static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? NMSPMM_OK : cuda_fail(e);
 }
 

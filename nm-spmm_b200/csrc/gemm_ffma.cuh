@@ -144,11 +144,11 @@ nm_gemm_ffma_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
         if (itl % NCW == warp) fill(itl);
     }
 
-    float acc[MT][8];
+    float2 acc[MT][4];                                     // row i, column pairs (0,1) (2,3) | (16,17) (18,19)
 #pragma unroll
     for (int i = 0; i < MT; ++i)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+        for (int j = 0; j < 4; ++j) acc[i][j] = make_float2(0.0f, 0.0f);
 
     const int q = bj / kVecLen + vec;                      // global vector number
     const int lb = q / g.qs_l - lb0;                       // index block of this vector, relative to the tile
@@ -163,6 +163,9 @@ nm_gemm_ffma_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
     for (int it = 0; it < nwin; ++it) {
         const int s = it % STAGES;
         const int nxt = it + STAGES - 1;
+#ifdef NMSPMM_FFMA_WINDOW_SYNC
+        __syncthreads();
+#endif
         if (nxt < nwin && it % NCW == warp) {
             if (!fill(nxt)) break;
         }
@@ -188,7 +191,8 @@ nm_gemm_ffma_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
             for (int p = 0; p < WS; ++p) row_off[p] *= (MS * 4);
 
-            float a[2][MT], b[2][8];
+            float a[2][MT];
+            float4 b[2][2];
             auto load = [&](int p, int buf) {
                 const unsigned char* ap = as + row_off[p];
                 if constexpr (MT == 8) {
@@ -200,19 +204,32 @@ nm_gemm_ffma_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
                     *reinterpret_cast<float2*>(&a[buf][0]) = *reinterpret_cast<const float2*>(ap);
                 }
                 const unsigned char* bp = bs + p * (NS * 4);
-                *reinterpret_cast<float4*>(&b[buf][0]) = *reinterpret_cast<const float4*>(bp);
-                *reinterpret_cast<float4*>(&b[buf][4]) = *reinterpret_cast<const float4*>(bp + 16 * 4);
+                b[buf][0] = *reinterpret_cast<const float4*>(bp);
+                b[buf][1] = *reinterpret_cast<const float4*>(bp + 16 * 4);
             };
             load(0, 0);
 #pragma unroll
             for (int p = 0; p < WS; ++p) {
                 if (p + 1 < WS) load(p + 1, (p + 1) & 1);
+                // Packed FP32 FMA (two lanes per instruction): the B pairs come straight
+                // out of the 128-bit loads, the A value is duplicated into a pair.  Each
+                // component rounds exactly like a scalar fmaf.
+                const float4 b0 = b[p & 1][0], b1 = b[p & 1][1];
+                const float2 bp0 = make_float2(b0.x, b0.y), bp1 = make_float2(b0.z, b0.w);
+                const float2 bp2 = make_float2(b1.x, b1.y), bp3 = make_float2(b1.z, b1.w);
 #pragma unroll
                 for (int i = 0; i < MT; ++i) {
-#pragma unroll
-                    for (int jj = 0; jj < 8; ++jj) {
-                        const int j = (i & 1) ? 7 - jj : jj;          // serpentine: neighbours share an operand register
-                        acc[i][j] = fmaf(a[p & 1][i], b[p & 1][j], acc[i][j]);
+                    const float2 aa = make_float2(a[p & 1][i], a[p & 1][i]);
+                    if (i & 1) {                                   // serpentine over the column pairs
+                        acc[i][3] = __ffma2_rn(aa, bp3, acc[i][3]);
+                        acc[i][2] = __ffma2_rn(aa, bp2, acc[i][2]);
+                        acc[i][1] = __ffma2_rn(aa, bp1, acc[i][1]);
+                        acc[i][0] = __ffma2_rn(aa, bp0, acc[i][0]);
+                    } else {
+                        acc[i][0] = __ffma2_rn(aa, bp0, acc[i][0]);
+                        acc[i][1] = __ffma2_rn(aa, bp1, acc[i][1]);
+                        acc[i][2] = __ffma2_rn(aa, bp2, acc[i][2]);
+                        acc[i][3] = __ffma2_rn(aa, bp3, acc[i][3]);
                     }
                 }
             }
@@ -237,8 +254,8 @@ nm_gemm_ffma_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
                 const int r = row_of(i);
                 if (r < g.M) {
                     float* cp = g.C + static_cast<size_t>(r) * g.N + col0;
-                    *reinterpret_cast<float4*>(cp) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
-                    *reinterpret_cast<float4*>(cp + 16) = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+                    *reinterpret_cast<float4*>(cp) = make_float4(acc[i][0].x, acc[i][0].y, acc[i][1].x, acc[i][1].y);
+                    *reinterpret_cast<float4*>(cp + 16) = make_float4(acc[i][2].x, acc[i][2].y, acc[i][3].x, acc[i][3].y);
                 }
             }
         }
@@ -252,8 +269,8 @@ nm_gemm_ffma_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
         float4* mine = part + static_cast<size_t>(z) * E * NCT + tid;
 #pragma unroll
         for (int i = 0; i < MT; ++i) {
-            __stcg(mine + (2 * i) * NCT, make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]));
-            __stcg(mine + (2 * i + 1) * NCT, make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]));
+            __stcg(mine + (2 * i) * NCT, make_float4(acc[i][0].x, acc[i][0].y, acc[i][1].x, acc[i][1].y));
+            __stcg(mine + (2 * i + 1) * NCT, make_float4(acc[i][2].x, acc[i][2].y, acc[i][3].x, acc[i][3].y));
         }
     }
     __threadfence();

@@ -27,6 +27,7 @@ const FfmaVariant* find_ffma_variant(int tile_id, int ws, int mode);
 // elements outside the tensor are delivered as zeros.
 cudaError_t encode_tensor_map_2d(CUtensorMap* map, const float* base, int cols, int rows, int box_cols, int box_rows);
 
-cudaError_t measure_ffma_peak(double* tflops, cudaStream_t st);
+// packed = 0: scalar FFMA loop; 1: two-lane packed FFMA2 loop.
+cudaError_t measure_ffma_peak(double* tflops, int packed, cudaStream_t st);
 
 }  // namespace nmspmm

@@ -24,7 +24,26 @@ __global__ void __launch_bounds__(512) ffma_peak_kernel(float* sink, float x, fl
     if (s == 123.456f) *sink = s;       // never true in practice; keeps the loop alive
 }
 
-cudaError_t measure_ffma_peak(double* tflops, cudaStream_t st)
+// The same loop with the packed two-lane FMA of sm_100.
+__global__ void __launch_bounds__(512) ffma2_peak_kernel(float* sink, float x, float y)
+{
+    float2 acc[kProbeChains / 2];
+#pragma unroll
+    for (int c = 0; c < kProbeChains / 2; ++c) acc[c] = make_float2(x * (threadIdx.x + c), x * (threadIdx.x - c));
+    const float2 yy = make_float2(y, y), xx = make_float2(x, x);
+    for (int it = 0; it < kProbeIters; ++it) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+#pragma unroll
+            for (int c = 0; c < kProbeChains / 2; ++c) acc[c] = __ffma2_rn(acc[c], yy, xx);
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int c = 0; c < kProbeChains / 2; ++c) s += acc[c].x + acc[c].y;
+    if (s == 123.456f) *sink = s;
+}
+
+cudaError_t measure_ffma_peak(double* tflops, int packed, cudaStream_t st)
 {
     int dev = 0, sms = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -41,7 +60,10 @@ cudaError_t measure_ffma_peak(double* tflops, cudaStream_t st)
     double best = 0.0;
     for (int rep = 0; rep < 6; ++rep) {
         cudaEventRecord(t0, st);
-        ffma_peak_kernel<<<blocks, threads, 0, st>>>(sink, 0.999f, 1.0001f);
+        if (packed)
+            ffma2_peak_kernel<<<blocks, threads, 0, st>>>(sink, 0.999f, 1.0001f);
+        else
+            ffma_peak_kernel<<<blocks, threads, 0, st>>>(sink, 0.999f, 1.0001f);
         cudaEventRecord(t1, st);
         e = cudaEventSynchronize(t1);
         if (e != cudaSuccess) break;
