@@ -282,7 +282,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         if rank == 0:
             print(json.dumps({"kernel_only": True, "ffma_peak": [pkg.measure_ffma_peak(False), pkg.measure_ffma_peak(True)],
                               "n_keep": keep, "ms_per_step": ms_per_step, "useful_tflops": value,
-                              "tile": [plan.tile_m, plan.tile_n], "split_k": plan.split_k, "stages": plan.stages,
+                              "tile": [plan.tile_m, plan.tile_n], "split_k": plan.split_k, "grid": plan.grid, "stages": plan.stages,
                               "clocks": sampler.summary()}), flush=True)
         if world > 1:
             dist.destroy_process_group()
@@ -311,8 +311,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                        "nominal 148 SMs x 128 lanes x 2 x SM clock",
         "algorithmic_bytes": abytes, "algorithmic_flops": useful,
         "hbm_time_us": t_mem * 1e6, "hbm_peak_gbs": hbm_gbs, "hbm_peak_source": hbm_src,
-        "kernel": f"nm_gemm_ffma_kernel tile {plan.tile_m}x{plan.tile_n}, split_k {plan.split_k}, "
-                  f"{plan.stages} stages, {plan.smem_bytes} B smem, grid {plan.grid_x}x{plan.grid_y}x{plan.grid_z}",
+        "kernel": f"nm_gemm_ffma_kernel tile {plan.tile_m}x{plan.tile_n}, "
+                  f"{'stream-K' if plan.stream_k else 'split_k ' + str(plan.split_k)}: {plan.tiles_x * plan.tiles_y} tiles in "
+                  f"{plan.n_virtual} ranges on {plan.grid} resident CTAs, {plan.stages} stages, {plan.smem_bytes} B smem",
         "kernel_ms": ms_per_step,
     }
 

@@ -100,18 +100,19 @@ typedef struct nmspmm_gemm_desc {
     int format;        /* nmspmm_format */
     int layout_ns;     /* Ns the index buffers were packed for: 32, 64 or 128 */
     int path;          /* nmspmm_path */
-    int split_k;       /* >=1: number of K slices; 0: chosen by the library */
+    int split_k;       /* >=1: that many K slices per tile; 0: the library balances k windows over the SMs */
     int tile;          /* 0: chosen by the library; otherwise an nmspmm_tile id (testing / tuning) */
 } nmspmm_gemm_desc;
 
-/* Bytes of scratch the multiply needs for this description (0 when split_k resolves to 1).
- * The scratch holds split-K partial tiles and per-tile arrival counters; the counters
- * must be zero before the first use (cudaMemset once) and are left zero by every call. */
+/* Bytes of scratch the multiply needs for this description (0 when every unit range is a
+ * whole tile).  The scratch holds per-tile arrival counters followed by slots for tile
+ * pieces; the counters must be zero before the first use (cudaMemset once) and are
+ * left zero by every call. */
 size_t nmspmm_gemm_workspace_bytes(const nmspmm_gemm_desc* desc);
 
 /* Replaces the eight nmGEMM_*_matrices_{low,high}_sparsity launchers
  * (src/kernel_*.cu).  C is overwritten with A.B for every split_k (deterministic:
- * partials are summed in slice order by the last tile to arrive).  Asynchronous on
+ * the pieces of a tile are summed in k order by the last one to arrive).  Asynchronous on
  * `stream`.  column_info_dev is NULL for NMSPMM_FORMAT_LOW. */
 int nmspmm_gemm(const nmspmm_gemm_desc* desc,
                 const float* A_dev, const float* B_dev, const int* D_dev, const int* column_info_dev,
@@ -133,8 +134,12 @@ int nmspmm_device_status(int* status_out, int clear);
 typedef struct nmspmm_gemm_plan_info {
     int tile;          /* nmspmm_tile id */
     int tile_m, tile_n;
-    int split_k;
-    int grid_x, grid_y, grid_z;
+    int split_k;       /* explicit: K slices per tile; automatic: ranges per tile of the balanced tail, rounded up */
+    int tiles_x, tiles_y;
+    int n_virtual;     /* contiguous unit ranges the work is cut into (= CTAs launched) */
+    int grid;          /* CTAs launched */
+    int stream_k;      /* 1: automatic schedule (whole tiles + balanced tail); 0: explicit split */
+    int n_dp;          /* automatic: leading tiles computed whole by one CTA each */
     int threads;
     int smem_bytes;
     int stages;

@@ -21,7 +21,8 @@ import numpy as np
 from . import build, formats, sharding  # noqa: F401  (in-tree nvcc build; seeded operands; multi-GPU partition)
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libnmspmm_b200.so")
+# NMSPMM_LIBRARY selects another build of the same library (A/B comparisons of kernels).
+LIB_PATH = os.environ.get("NMSPMM_LIBRARY") or os.path.join(_HERE, "libnmspmm_b200.so")
 
 OK, INVALID_ARGUMENT, UNSUPPORTED, CUDA_ERROR, WORKSPACE_TOO_SMALL, DEVICE_TIMEOUT = range(6)
 PATH_FP32, PATH_TF32 = 0, 1
@@ -45,7 +46,8 @@ class GemmDesc(ctypes.Structure):
 
 class PlanInfo(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int) for n in
-                ("tile", "tile_m", "tile_n", "split_k", "grid_x", "grid_y", "grid_z", "threads", "smem_bytes", "stages")]
+                ("tile", "tile_m", "tile_n", "split_k", "tiles_x", "tiles_y", "n_virtual", "grid", "stream_k",
+                 "n_dp", "threads", "smem_bytes", "stages")]
 
 
 class NMSpMMError(RuntimeError):

@@ -9,8 +9,8 @@ import subprocess
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
-OBJ = os.path.join(CSRC, "build")
-LIB = os.path.join(HERE, "libnmspmm_b200.so")
+OBJ = os.environ.get("NMSPMM_BUILD_DIR") or os.path.join(CSRC, "build")
+LIB = os.environ.get("NMSPMM_BUILD_LIB") or os.path.join(HERE, "libnmspmm_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "-I" + os.path.join(ROOT, "include"), "-I" + CSRC] + os.environ.get("NMSPMM_NVCC_EXTRA", "").split()

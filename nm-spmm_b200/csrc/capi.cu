@@ -17,18 +17,18 @@ NMSPMM_VARIANT_TABLE(low32)
 NMSPMM_VARIANT_TABLE(low16)
 NMSPMM_VARIANT_TABLE(low12)
 NMSPMM_VARIANT_TABLE(low8)
-NMSPMM_VARIANT_TABLE(high16)
 NMSPMM_VARIANT_TABLE(high8)
+NMSPMM_VARIANT_TABLE(high4)
 
-const FfmaVariant* find_ffma_variant(int tile_id, int ws, int mode)
+const FfmaVariant* find_ffma_variant(int tile_id, int n_keep, int mode)
 {
     struct Table { const FfmaVariant* v; int n; };
     const Table tables[] = { { kFfma_low32, kFfma_low32_count }, { kFfma_low16, kFfma_low16_count },
                              { kFfma_low12, kFfma_low12_count }, { kFfma_low8, kFfma_low8_count },
-                             { kFfma_high16, kFfma_high16_count }, { kFfma_high8, kFfma_high8_count } };
+                             { kFfma_high8, kFfma_high8_count }, { kFfma_high4, kFfma_high4_count } };
     for (const Table& t : tables)
         for (int i = 0; i < t.n; ++i)
-            if (t.v[i].tile_id == tile_id && t.v[i].ws == ws && t.v[i].mode == mode) return &t.v[i];
+            if (t.v[i].tile_id == tile_id && t.v[i].n_keep == n_keep && t.v[i].mode == mode) return &t.v[i];
     return nullptr;
 }
 
@@ -51,6 +51,9 @@ struct DeviceInfo {
 static DeviceInfo g_dev[64];
 static std::mutex g_dev_mutex;
 __device__ int g_status_word;      // raised by kernels whose bounded waits gave up
+#ifdef NMSPMM_PROFILE_WAITS
+__device__ unsigned long long g_wait_profile[4];   // diagnostic build: wait, fill, total cycles of warp 0, CTA count
+#endif
 
 static int device_info(DeviceInfo** out)
 {
@@ -76,12 +79,17 @@ static int device_info(DeviceInfo** out)
 // ---- plan -----------------------------------------------------------------------
 struct Plan {
     const FfmaVariant* v = nullptr;
-    int W = 0, ws = 0, n_win = 0, split_k = 1;
-    dim3 grid;
+    int W = 0, ws = 0, n_win = 0;
+    int tiles_x = 0, tiles_y = 0, n_tiles = 0;
+    int split_k = 0;        // > 0 explicit slices per tile, 0 automatic
+    int n_dp = 0;           // automatic: leading tiles computed whole
+    int n_virtual = 0;      // unit ranges (= CTAs)
+    int slots = 0;          // scratch slots for tile pieces
+    int grid = 0;           // resident CTAs launched
     size_t counters_bytes = 0, partial_bytes = 0;
 };
 
-static int check_desc(const nmspmm_gemm_desc* d, int* ws_out, int* mode_out)
+static int check_desc(const nmspmm_gemm_desc* d, int* mode_out)
 {
     if (!d) return NMSPMM_INVALID_ARGUMENT;
     if (d->M <= 0 || d->N <= 0 || d->K <= 0) return NMSPMM_INVALID_ARGUMENT;
@@ -91,12 +99,10 @@ static int check_desc(const nmspmm_gemm_desc* d, int* ws_out, int* mode_out)
     if (d->split_k < 0) return NMSPMM_INVALID_ARGUMENT;
     if (d->format == NMSPMM_FORMAT_LOW) {
         if (d->n_keep != 32 && d->n_keep != 16 && d->n_keep != 12 && d->n_keep != 8) return NMSPMM_UNSUPPORTED;
-        *ws_out = d->n_keep;
         *mode_out = kModeLow;
     } else if (d->format == NMSPMM_FORMAT_HIGH) {
         if (d->n_keep != 8 && d->n_keep != 4) return NMSPMM_UNSUPPORTED;
         if (d->K % 64 != 0) return NMSPMM_INVALID_ARGUMENT;
-        *ws_out = 2 * d->n_keep;
         *mode_out = kModeHigh;
     } else {
         return NMSPMM_INVALID_ARGUMENT;
@@ -106,54 +112,72 @@ static int check_desc(const nmspmm_gemm_desc* d, int* ws_out, int* mode_out)
 
 static int pick_tile(const nmspmm_gemm_desc* d, int sms)
 {
+    (void)sms;
     if (d->M <= 16) return kTile16x128;
     if (d->M <= 32) return kTile32x128;
     if (d->M <= 64) return kTile64x128;
     const int pad128 = (d->M + 127) / 128 * 128, pad64 = (d->M + 63) / 64 * 64;
-    if (pad64 < pad128) return kTile64x128;
-    // The widest tile reads the A window once for eight vectors; use it when it still
-    // gives every SM at least two tiles.
-    const long long wide = static_cast<long long>((d->M + 127) / 128) * ((d->N + 255) / 256);
-    return (wide >= 2LL * sms) ? kTile128x256 : kTile128x128;
+    return (pad64 < pad128) ? kTile64x128 : kTile128x128;
 }
 
 static int make_plan(const nmspmm_gemm_desc* d, int sms, Plan* p)
 {
-    int ws = 0, mode = 0;
-    int rc = check_desc(d, &ws, &mode);
+    int mode = 0;
+    int rc = check_desc(d, &mode);
     if (rc != NMSPMM_OK) return rc;
     if (d->path != NMSPMM_PATH_FP32) return NMSPMM_UNSUPPORTED;
-    const int tile = d->tile ? d->tile : pick_tile(d, sms > 0 ? sms : 148);
-    const FfmaVariant* v = find_ffma_variant(tile, ws, mode);
+    if (sms <= 0) sms = 148;
+    const int tile = d->tile ? d->tile : pick_tile(d, sms);
+    const FfmaVariant* v = find_ffma_variant(tile, d->n_keep, mode);
     if (!v) return NMSPMM_UNSUPPORTED;
     p->v = v;
-    p->ws = ws;
+    p->ws = v->ws;
+    const int ws = v->ws;
     p->W = d->K / 32 * d->n_keep;
     p->n_win = p->W / ws;
-    const int gx = (d->N + v->ns - 1) / v->ns, gy = (d->M + v->ms - 1) / v->ms;
-    if (gy > 65535) return NMSPMM_UNSUPPORTED;
-    int split = d->split_k;
-    if (split == 0) {
-        // Fill the machine: as many slices as leave every resident CTA slot one unit of
-        // work, but at least four windows per slice.
-        const long long tiles = static_cast<long long>(gx) * gy;
-        const long long slots = static_cast<long long>(sms > 0 ? sms : 148) * v->min_blocks;
-        long long s = slots / tiles;
-        if (s < 1) s = 1;
-        const long long cap = p->n_win / 4 > 0 ? p->n_win / 4 : 1;
-        if (s > cap) s = cap;
-        if (s > 64) s = 64;
-        split = static_cast<int>(s);
+    p->tiles_x = (d->N + v->ns - 1) / v->ns;
+    p->tiles_y = (d->M + v->ms - 1) / v->ms;
+    const long long n_tiles = static_cast<long long>(p->tiles_x) * p->tiles_y;
+    const long long units = n_tiles * p->n_win;
+    if (units >= (1LL << 31) || n_tiles >= (1LL << 28)) return NMSPMM_UNSUPPORTED;
+    p->n_tiles = static_cast<int>(n_tiles);
+    const int resident = sms * v->min_blocks;
+    if (d->split_k > 0) {
+        // Explicit K slices: one unit range per (tile, slice); a single slice stores directly.
+        int s = d->split_k < p->n_win ? d->split_k : p->n_win;
+        if (n_tiles * s >= (1LL << 31)) return NMSPMM_UNSUPPORTED;
+        p->split_k = s;
+        p->n_virtual = static_cast<int>(n_tiles * s);
+        p->slots = (s > 1) ? p->n_virtual : 0;
+    } else {
+        // Automatic: whole tiles for as many complete waves of resident CTAs as there are,
+        // then the units of the remaining tiles in equal ranges, one per resident CTA, each
+        // at least four windows long where the problem allows (never less than one).
+        // (With two or more complete waves the whole-tile grid is used as it is: measured
+        // on 4096^3, the partial last wave costs less than the split tiles' round trip
+        // through scratch, because a CTA that has an SM to itself runs faster.)
+        const long long n_dp = (n_tiles >= 2LL * resident) ? n_tiles : n_tiles / resident * resident;
+        const long long tail_tiles = n_tiles - n_dp;
+        long long n_sk = 0;
+        if (tail_tiles > 0) {
+            const long long tail_units = tail_tiles * p->n_win;
+            n_sk = resident;
+            const long long by_length = tail_units / 4 > tail_tiles ? tail_units / 4 : tail_tiles;
+            if (n_sk > by_length) n_sk = by_length;
+            if (n_sk > tail_units) n_sk = tail_units;
+            if (n_sk < 1) n_sk = 1;
+        }
+        p->split_k = 0;
+        p->n_dp = static_cast<int>(n_dp);
+        p->n_virtual = static_cast<int>(n_dp + n_sk);
+        // equal ranges that coincide with whole tiles need no scratch
+        const bool aligned = (n_sk == 0) || (n_sk == tail_tiles);
+        p->slots = aligned ? 0 : static_cast<int>(2 * n_sk);
     }
-    if (split > p->n_win) split = p->n_win;
-    if (split < 1) split = 1;
-    if (split > 65535) return NMSPMM_UNSUPPORTED;
-    p->split_k = split;
-    p->grid = dim3(gx, gy, split);
-    if (split > 1) {
-        const size_t tiles = static_cast<size_t>(gx) * gy;
-        p->counters_bytes = (tiles * sizeof(unsigned) + 255) / 256 * 256;
-        p->partial_bytes = tiles * split * static_cast<size_t>(v->ms) * v->ns * sizeof(float);
+    p->grid = p->n_virtual;      // one unit range per CTA (the automatic schedule never exceeds the resident count)
+    if (p->slots > 0) {
+        p->counters_bytes = (static_cast<size_t>(p->n_tiles) * sizeof(unsigned) + 255) / 256 * 256;
+        p->partial_bytes = static_cast<size_t>(p->slots) * v->ms * v->ns * sizeof(float);
     }
     return NMSPMM_OK;
 }
@@ -370,10 +394,14 @@ int nmspmm_gemm_plan(const nmspmm_gemm_desc* desc, nmspmm_gemm_plan_info* out)
     out->tile = p.v->tile_id;
     out->tile_m = p.v->ms;
     out->tile_n = p.v->ns;
-    out->split_k = p.split_k;
-    out->grid_x = p.grid.x;
-    out->grid_y = p.grid.y;
-    out->grid_z = p.grid.z;
+    out->split_k = p.split_k > 0 ? p.split_k
+                                 : (p.n_tiles > p.n_dp ? (p.n_virtual - p.n_dp + p.n_tiles - p.n_dp - 1) / (p.n_tiles - p.n_dp) : 1);
+    out->n_dp = p.n_dp;
+    out->tiles_x = p.tiles_x;
+    out->tiles_y = p.tiles_y;
+    out->n_virtual = p.n_virtual;
+    out->grid = p.grid;
+    out->stream_k = p.split_k > 0 ? 0 : 1;
     out->threads = p.v->threads;
     out->smem_bytes = p.v->smem_bytes;
     out->stages = p.v->stages;
@@ -402,10 +430,14 @@ int nmspmm_gemm(const nmspmm_gemm_desc* desc, const float* A_dev, const float* B
     a.M = desc->M;
     a.N = desc->N;
     a.W = p.W;
-    a.n_win = p.n_win;
-    a.split_k = p.split_k;
-    a.qs_l = desc->layout_ns / kVecLenHost;
-    if (p.split_k > 1) {
+    a.tiles_x = p.tiles_x;
+    a.sched.n_tiles = p.n_tiles;
+    a.sched.n_win = p.n_win;
+    a.sched.n_virtual = p.n_virtual;
+    a.sched.split_k = p.split_k;
+    a.sched.n_dp = p.n_dp;
+    a.qs_shift = desc->layout_ns == 128 ? 2 : (desc->layout_ns == 64 ? 1 : 0);
+    if (p.slots > 0) {
         if (!workspace_dev || !aligned16(workspace_dev)) return NMSPMM_INVALID_ARGUMENT;
         if (workspace_bytes < p.counters_bytes + p.partial_bytes) return NMSPMM_WORKSPACE_TOO_SMALL;
         a.counters = static_cast<unsigned*>(workspace_dev);
@@ -494,6 +526,18 @@ int nmspmm_gemm_host(const nmspmm_gemm_desc* desc, const float* A_host, const fl
     if ((e = cudaStreamSynchronize(st)) != cudaSuccess) return cuda_fail(e);
     return nmspmm_device_status(nullptr, 1);
 }
+
+#ifdef NMSPMM_PROFILE_WAITS
+// Diagnostic build only: reads and clears the cycle counters.
+int nmspmm_debug_wait_profile(unsigned long long* out4)
+{
+    cudaError_t e = cudaMemcpyFromSymbol(out4, g_wait_profile, sizeof(unsigned long long) * 4);
+    if (e != cudaSuccess) return cuda_fail(e);
+    unsigned long long zero[4] = { 0, 0, 0, 0 };
+    e = cudaMemcpyToSymbol(g_wait_profile, zero, sizeof(zero));
+    return e == cudaSuccess ? NMSPMM_OK : cuda_fail(e);
+}
+#endif
 
 int nmspmm_release_cached(void)
 {

@@ -34,6 +34,13 @@ __device__ __forceinline__ void mbar_init_fence()
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// Orders this thread's earlier generic-proxy accesses to shared memory before later
+// asynchronous-proxy (TMA) accesses.
+__device__ __forceinline__ void fence_proxy_async()
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 __device__ __forceinline__ void mbar_arrive(uint32_t bar)
 {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -59,19 +66,33 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 
+__device__ __forceinline__ int lds_volatile_s32(uint32_t addr)
+{
+    int v;
+    asm volatile("ld.volatile.shared.s32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void sts_volatile_s32(uint32_t addr, int v)
+{
+    asm volatile("st.volatile.shared.s32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+
 // Waits for the phase with the given parity to complete.  Gives up after
-// kWaitCycleLimit cycles, or as soon as another thread of the CTA has given up
-// (*abort_flag != 0); returns false in both cases and raises the flag.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag)
+// kWaitCycleLimit cycles, or as soon as another thread of the CTA has given up (the
+// word at shared address abort_word is non-zero); returns false in both cases and
+// raises the word.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t abort_word)
 {
     if (mbar_try_wait(bar, parity)) return true;
+    if (lds_volatile_s32(abort_word)) return false;
     const long long t0 = clock64();
     unsigned spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 255u) == 0u) {
-            if (*abort_flag) return false;
+            if (lds_volatile_s32(abort_word)) return false;
             if (clock64() - t0 > kWaitCycleLimit) {
-                *abort_flag = 1;
+                sts_volatile_s32(abort_word, 1);
                 return false;
             }
         }
@@ -99,19 +120,27 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void* tenso
         : "memory");
 }
 
-// Which windows (of n_win) slice z of split_k owns: the first n_win % split_k
-// slices get one extra window (the split of src/kernel_64x128_8x8.cu:21-37 of the
-// reference, kept so that a given SPLIT_K covers the same k ranges).
-__host__ __device__ __forceinline__ void slice_range(int n_win, int split_k, int z, int& first, int& count)
+// Shared-memory loads by 32-bit shared address.  volatile: they stay behind the
+// mbarrier wait that guards the stage they read.
+__device__ __forceinline__ float4 lds_f4(uint32_t addr)
 {
-    const int base = n_win / split_k, rem = n_win % split_k;
-    if (z < rem) {
-        count = base + 1;
-        first = z * (base + 1);
-    } else {
-        count = base;
-        first = rem * (base + 1) + (z - rem) * base;
-    }
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ float2 lds_f2(uint32_t addr)
+{
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ int lds_s32(uint32_t addr)
+{
+    int v;
+    asm volatile("ld.shared.s32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
 }
 
 }  // namespace nmspmm

@@ -1,5 +1,12 @@
-// Kernel argument block of the multiply (plain data, usable from host code).
+// Kernel argument block of the multiply and the unit schedule shared by host and
+// device (plain data and integer arithmetic, usable from host code).
 #pragma once
+
+#if defined(__CUDACC__)
+#define NMSPMM_HD __host__ __device__ __forceinline__
+#else
+#define NMSPMM_HD inline
+#endif
 
 namespace nmspmm {
 
@@ -17,19 +24,94 @@ enum nmspmm_tile {
     kTileCount
 };
 
+// The unit schedule.  Units are numbered tile * n_win + window.
+//   split_k > 0 : range v = K slice (v % split_k) of tile (v / split_k).
+//   split_k == 0: the first n_dp ranges are the first n_dp tiles, whole (they run as
+//                 ordinary full waves and keep neighbouring CTAs on neighbouring tiles
+//                 and k windows, which is what the L2 likes); the units of the
+//                 remaining tiles are cut into n_virtual - n_dp equal ranges that
+//                 fill the last, partial wave evenly.
+struct UnitSchedule {
+    int n_tiles, n_win, n_virtual, split_k, n_dp;
+};
+
 struct GemmArgs {
     const float* A;
     const float* B;
     const int* D;
     const int* cinfo;
     float* C;
-    float* partial;        // split-K scratch, [tile][slice][float4 e][thread]
+    float* partial;        // scratch slots of tile pieces, [slot][float4 e][thread]
     unsigned* counters;    // one per tile, zero between calls
     int* status;           // device status word (0 = ok)
     int M, N, W;
-    int n_win;             // W / WS
-    int split_k;
-    int qs_l;              // vectors per packed index block (layout_ns / 32)
+    int tiles_x;           // tiles per row of tiles
+    UnitSchedule sched;    // n_tiles, n_win (k windows per tile, W / WS), ranges
+    int qs_shift;          // log2 of the vectors per packed index block (layout_ns / 32): 0, 1 or 2
 };
+
+// Which windows (of n_win) slice z of split_k owns: the first n_win % split_k
+// slices get one extra window (the split of src/kernel_64x128_8x8.cu:21-37 of the
+// reference, kept so that a given SPLIT_K covers the same k ranges).
+NMSPMM_HD void slice_range(int n_win, int split_k, int z, int& first, int& count)
+{
+    const int base = n_win / split_k, rem = n_win % split_k;
+    if (z < rem) {
+        count = base + 1;
+        first = z * (base + 1);
+    } else {
+        count = base;
+        first = rem * (base + 1) + (z - rem) * base;
+    }
+}
+
+// Units of virtual CTA v: [u0, u1).
+NMSPMM_HD void virtual_range(const UnitSchedule& sc, int v, long long& u0, long long& u1)
+{
+    if (sc.split_k > 0) {
+        int first, count;
+        slice_range(sc.n_win, sc.split_k, v % sc.split_k, first, count);
+        u0 = static_cast<long long>(v / sc.split_k) * sc.n_win + first;
+        u1 = u0 + count;
+    } else if (v < sc.n_dp) {
+        u0 = static_cast<long long>(v) * sc.n_win;
+        u1 = u0 + sc.n_win;
+    } else {
+        const long long base = static_cast<long long>(sc.n_dp) * sc.n_win;
+        const long long total = static_cast<long long>(sc.n_tiles - sc.n_dp) * sc.n_win;
+        const int n_sk = sc.n_virtual - sc.n_dp;
+        u0 = base + (v - sc.n_dp) * total / n_sk;
+        u1 = base + (v - sc.n_dp + 1) * total / n_sk;
+    }
+}
+
+// First and last virtual CTA holding a piece of `tile` (consecutive; every one in
+// between holds a piece too, provided the equal ranges are not more than the units).
+NMSPMM_HD void tile_contributors(const UnitSchedule& sc, int tile, int& v_first, int& v_last)
+{
+    if (sc.split_k > 0) {
+        v_first = tile * sc.split_k;
+        v_last = v_first + sc.split_k - 1;
+    } else if (tile < sc.n_dp) {
+        v_first = v_last = tile;
+    } else {
+        const long long total = static_cast<long long>(sc.n_tiles - sc.n_dp) * sc.n_win;
+        const int n_sk = sc.n_virtual - sc.n_dp;
+        const long long x0 = static_cast<long long>(tile - sc.n_dp) * sc.n_win, x1 = x0 + sc.n_win - 1;
+        v_first = sc.n_dp + static_cast<int>(((x0 + 1) * n_sk - 1) / total);
+        v_last = sc.n_dp + static_cast<int>(((x1 + 1) * n_sk - 1) / total);
+    }
+}
+
+// Scratch slot of the piece of `tile` held by range v.  Explicit split: one slot per
+// range.  Automatic: two per equal range, the second for a tile that the range
+// entered part-way through its own course (it started in an earlier tile).
+NMSPMM_HD long long piece_slot(const UnitSchedule& sc, int v, int tile)
+{
+    if (sc.split_k > 0) return v;
+    long long u0, u1;
+    virtual_range(sc, v, u0, u1);
+    return 2LL * (v - sc.n_dp) + ((u0 < static_cast<long long>(tile) * sc.n_win) ? 1 : 0);
+}
 
 }  // namespace nmspmm

@@ -1,28 +1,36 @@
-// Exact-FP32 vector-wise N:M sparse GEMM for sm_100a.
+// Exact-FP32 vector-wise N:M sparse GEMM for sm_100a: persistent, stream-K scheduled.
 //
-// One CTA computes an MS x NS tile of C over a contiguous range of k windows
-// (its split-K slice).  Each window's operands are streamed into a STAGES-deep
-// shared-memory ring by the TMA engine, completion counted on mbarriers: one tiled
-// tensor copy for the window of A, one for the window of B, and small bulk copies
-// for the indices.  The warps take turns issuing a window's copies (a few
-// instructions by one warp per window) and otherwise only compute: there is no
-// CTA-wide barrier in the main loop.  Per window the ring holds
+// Work is measured in units of one k window of one MS x NS tile of C, numbered tile
+// by tile.  The units are cut into contiguous ranges, one per CTA:
+//   * automatic schedule: as many whole tiles as fill complete waves of resident
+//     CTAs, then the units of the remaining tiles in equal ranges, one per resident
+//     CTA, so the last wave is as full as the others (no partial last wave);
+//   * explicit split_k = S: one range per (tile, K slice), as the reference's
+//     gridDim.z slices (src/kernel_64x128_8x8.cu:17-37).
+// A CTA walks its range window by window.  Each window's operands are streamed into
+// a STAGES-deep shared-memory ring by the TMA engine, completion counted on
+// mbarriers: one tiled tensor copy for the window of A, one for the window of B, and
+// small bulk copies for the indices.  The ring runs across tile boundaries, so the
+// next tile's operands arrive while the current tile is finished and stored.  One
+// CTA barrier per window keeps the warps in step and frees the previous window's
+// stage, which the warps take turns refilling.  Per window the ring holds
 //     As  [KS][MS]   the dense k window of A (A is col-major, so k-row r is MS
-//                    contiguous floats): 32 rows (LOW) or 64 rows (HIGH)
+//                    contiguous floats): 32 rows; HIGH pairs of windows share one
+//                    column_info list and may be staged as one 64-row window
 //     Bs  [WS][NS]   the window's compressed rows of B
 //     Ds  [..]       the window's packed indices for the vectors of the tile
 //     Cs  [..][64]   HIGH only: the window's column_info lists of the index blocks
 //                    under the tile; a packed index is a rank into its block's list
 // and the gather of the reference (src/kernel_64x128_8x8.cu:139-159) stays what it
 // was: the shared-memory row address As[k(p)].  Every warp owns one 32-column
-// vector, so that row is warp-uniform, and the 8x8 register tile reads two 128-bit
-// words of A and two of B per 64 FFMAs.  Unlike the reference's high-sparsity
-// kernels the A window is staged dense (one TMA box instead of one copy per used
-// column), which frees the CTA tile from the packed index block size.
+// vector, so that row is warp-uniform; the 8x8 register tile reads two 128-bit words
+// of A and two of B per 32 packed two-lane FMAs (64 FMAs).  Unlike the reference's
+// high-sparsity kernels the A window is staged dense (one TMA box instead of one
+// copy per used column), which frees the CTA tile from the packed index block size.
 //
-// split_k > 1: each slice writes its partial tile to scratch; the last slice to
-// arrive (per-tile counter) adds the partials in slice order and writes C, so the
-// result does not depend on arrival order.
+// A range that covers a whole tile stores C directly.  Otherwise the piece goes to
+// a scratch slot; the last piece of a tile to arrive (per-tile counter) adds the
+// pieces in k order and writes C, so the result does not depend on arrival order.
 #pragma once
 #include <cuda.h>
 
@@ -32,9 +40,22 @@
 
 namespace nmspmm {
 
-template <int MS, int NS, int WM, int WS, int MODE>
+// Diagnostic build (-DNMSPMM_PROFILE_WAITS): warp 0 of every CTA adds up the cycles
+// it spends waiting for a filled stage, filling a stage, and in total.
+#ifdef NMSPMM_PROFILE_WAITS
+extern __device__ unsigned long long g_wait_profile[4];
+#define NMSPMM_PROF_T(var) const long long var = clock64()
+#define NMSPMM_PROF_ADD(acc, t0) acc += clock64() - (t0)
+#else
+#define NMSPMM_PROF_T(var)
+#define NMSPMM_PROF_ADD(acc, t0)
+#endif
+
+template <int MS, int NS, int WM, int WS, int KS_, int MODE>
 struct FfmaCfg {
-    static constexpr int KS = (MODE == kModeLow) ? 32 : 64;
+    static constexpr int KS = KS_;                       // rows of A staged per window: 32, or 64 (a merged HIGH window)
+    static constexpr bool HALF = (MODE == kModeHigh && KS_ == 32);   // HIGH staged by halves of the merged window
+    static_assert(MODE == kModeHigh || KS_ == 32, "LOW windows are 32 k wide");
     static constexpr int QT = NS / kVecLen;              // vectors per tile
     static constexpr int WARPS_M = MS / WM;
     static constexpr int NCW = QT * WARPS_M;             // warps (all of them compute)
@@ -53,202 +74,266 @@ struct FfmaCfg {
     static constexpr int BUDGET = (224 * 1024) / MIN_BLOCKS - 2048;
     static constexpr int ST0 = BUDGET / STAGE_BYTES;
     static constexpr int STAGES = ST0 < 2 ? 2 : (ST0 > 6 ? 6 : ST0);
-    static constexpr int BAR_BYTES = 128;                // 2*STAGES mbarriers + flags
+    static constexpr int BAR_BYTES = 128;                // STAGES mbarriers and two flag words
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 128;   // + alignment slack
     static_assert(MS % WM == 0 && (WM == 64 || WM == 32 || WM == 16), "warp tile");
-    static_assert(2 * STAGES * 8 + 16 <= BAR_BYTES, "barrier block");
+    static_assert(STAGES * 8 + 8 <= BAR_BYTES, "barrier block");
     static_assert(THREADS <= 512, "tile too large");
 };
 
-template <int MS, int NS, int WM, int WS, int MODE>
-__global__ void __launch_bounds__((FfmaCfg<MS, NS, WM, WS, MODE>::THREADS), (FfmaCfg<MS, NS, WM, WS, MODE>::MIN_BLOCKS))
+template <int MS, int NS, int WM, int WS, int KS_, int MODE>
+__global__ void __launch_bounds__((FfmaCfg<MS, NS, WM, WS, KS_, MODE>::THREADS), (FfmaCfg<MS, NS, WM, WS, KS_, MODE>::MIN_BLOCKS))
 nm_gemm_ffma_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b)
 {
-    using Cfg = FfmaCfg<MS, NS, WM, WS, MODE>;
+    using Cfg = FfmaCfg<MS, NS, WM, WS, KS_, MODE>;
     constexpr int KS = Cfg::KS, QT = Cfg::QT, NCW = Cfg::NCW, NCT = Cfg::NCT, MT = Cfg::MT, STAGES = Cfg::STAGES;
+    constexpr int E = MT * 2;                              // float4 words of C per thread
 
     extern __shared__ unsigned char smem_raw[];
-    // 128-byte aligned base (dynamic shared memory is only guaranteed 16).
-    unsigned char* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
-    unsigned char* ring = smem;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * STAGES);
-    volatile int* last_flag = abort_flag + 1;
+    // 128-byte aligned base (dynamic shared memory is only guaranteed 16); everything
+    // below is addressed by 32-bit shared addresses.
+    const uint32_t ring = (smem_u32(smem_raw) + 127u) & ~127u;
+    const uint32_t bars = ring + STAGES * Cfg::STAGE_BYTES;        // full[STAGES]: a stage's operands have landed
+    const uint32_t flags = bars + STAGES * 8;                      // abort word, last-piece word
+    const uint32_t abort_word = flags, last_word = flags + 4;
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
-    const int bj = blockIdx.x * NS;
-    const int bi = blockIdx.y * MS;
-    const int z = blockIdx.z;
-
-    int win0, nwin;
-    slice_range(g.n_win, g.split_k, z, win0, nwin);
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(smem_u32(&bars[s]), 1);              // full: one arrive (with expect_tx) by the filling warp
-            mbar_init(smem_u32(&bars[STAGES + s]), NCW);   // empty: one arrive per warp
+            mbar_init(bars + s * 8, 1);                    // full: one arrive (with expect_tx) by the filling warp
         }
-        *abort_flag = 0;
-        *last_flag = 0;
+        sts_volatile_s32(abort_word, 0);
+        sts_volatile_s32(last_word, 0);
         mbar_init_fence();
     }
     __syncthreads();
 
-    const int cols_here = min(NS, g.N - bj);               // columns of the tile that exist
-    const int layout_ns = g.qs_l * kVecLen;
-    const int lb0 = bj / layout_ns;                        // first packed index block under the tile
-    const int nlb = (bj + cols_here - 1) / layout_ns - lb0 + 1;
-    const int d_chunk = WS * g.qs_l;                       // ints of one block's window
-
+    const int qs_shift = g.qs_shift;                       // log2(vectors per packed index block)
+    const int layout_shift = qs_shift + 5;                 // log2(columns per packed index block)
+    const int d_chunk = WS << qs_shift;                    // ints of one index block's window
+    const uint32_t d_bytes = static_cast<uint32_t>(d_chunk) * 4u;
     const int vec = warp % QT, wm = warp / QT;
     const int lm = (lane & 15) >> 1;
-    const bool live = (vec * kVecLen < cols_here);         // vectors past N idle but keep the ring moving
+
+    // This CTA's unit range (one range per CTA: the grid has n_virtual CTAs).
+    int u_begin, u_end;
+    {
+        long long u0, u1;
+        virtual_range(g.sched, blockIdx.x, u0, u1);
+        u_begin = static_cast<int>(u0);
+        u_end = static_cast<int>(u1);
+    }
 
     // ---- filling one stage: the whole warp calls this (warp-uniform arguments) ----
-    // Window `itl` (relative to the slice) goes to stage itl % STAGES.  Returns false if
-    // the bounded wait for the stage's release gave up.
-    const uint32_t d_bytes = static_cast<uint32_t>(d_chunk) * 4u;
-    const uint32_t tx_bytes = Cfg::TX_FIXED + nlb * (d_bytes + (MODE == kModeHigh ? 256u : 0u));
-    auto fill = [&](int itl) -> bool {
-        const int s = itl % STAGES;
-        const int win = win0 + itl;
-        const uint32_t full = smem_u32(&bars[s]);
-        if (itl >= STAGES) {
-            const bool ok = mbar_wait_bounded(smem_u32(&bars[STAGES + s]), ((itl / STAGES) - 1) & 1, abort_flag);
-            if (!__all_sync(0xffffffffu, ok)) {            // the whole warp gives up together
-                if (lane == 0) atomicMax(g.status, kDevTimeoutEmpty);
-                return false;
-            }
-        }
-        const uint32_t as = smem_u32(ring + s * Cfg::STAGE_BYTES), bs = as + Cfg::A_BYTES, ds = bs + Cfg::B_BYTES;
+    // Unit `u` goes to stage s, which the caller knows to be free.
+    auto fill = [&](int s, int u) {
+        const uint32_t full = bars + s * 8;
+        const int tile = u / g.sched.n_win, win = u - tile * g.sched.n_win;
+        const int ty = tile / g.tiles_x, tx = tile - ty * g.tiles_x;
+        const int bj = tx * NS, bi = ty * MS;
+        const int cols = min(NS, g.N - bj);
+        const int lb0 = bj >> layout_shift;                // first packed index block under the tile
+        const int nlb = ((bj + cols - 1) >> layout_shift) - lb0 + 1;
+        const uint32_t as = ring + s * Cfg::STAGE_BYTES, bs = as + Cfg::A_BYTES, ds = bs + Cfg::B_BYTES;
         if (lane == 0) {
-            mbar_arrive_expect_tx(full, tx_bytes);
+            mbar_arrive_expect_tx(full, Cfg::TX_FIXED + nlb * (d_bytes + (MODE == kModeHigh ? 256u : 0u)));
             tma_load_2d(as, &map_a, bi, win * KS, full);      // rows/columns past the tensor arrive as zeros
             tma_load_2d(bs, &map_b, bj, win * WS, full);
         }
         __syncwarp();
         if (lane < nlb) {
-            const int* src = g.D + static_cast<size_t>(lb0 + lane) * g.W * g.qs_l + static_cast<size_t>(win) * d_chunk;
+            const int* src = g.D + ((static_cast<size_t>(lb0 + lane) * g.W) << qs_shift) + static_cast<size_t>(win) * d_chunk;
             bulk_g2s(ds + lane * d_bytes, src, d_bytes, full);
             if (MODE == kModeHigh) {
-                const int* ci = g.cinfo + (static_cast<size_t>(lb0 + lane) * g.n_win + win) * 64;
+                // one list per merged 64-k window: two staged windows share it when HALF
+                const int n_merged = Cfg::HALF ? (g.sched.n_win >> 1) : g.sched.n_win;
+                const int* ci = g.cinfo + (static_cast<size_t>(lb0 + lane) * n_merged + (Cfg::HALF ? (win >> 1) : win)) * 64;
                 bulk_g2s(ds + Cfg::D_BYTES + lane * 256, ci, 256, full);
             }
         }
-        return true;
     };
 
-    // Prologue: the first STAGES-1 windows, one filling warp each.
-    for (int itl = 0; itl < STAGES - 1 && itl < nwin; ++itl) {
-        if (itl % NCW == warp) fill(itl);
-    }
+    // Prologue: the first STAGES-1 windows, one filling warp each.  Window number j of the
+    // range (unit u_begin + j) always lives in stage j % STAGES.
+    for (int j = 0; j < STAGES - 1 && u_begin + j < u_end; ++j)
+        if (j % NCW == warp) fill(j, u_begin + j);
 
-    float2 acc[MT][4];                                     // row i, column pairs (0,1) (2,3) | (16,17) (18,19)
-#pragma unroll
-    for (int i = 0; i < MT; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = make_float2(0.0f, 0.0f);
-
-    const int q = bj / kVecLen + vec;                      // global vector number
-    const int lb = q / g.qs_l - lb0;                       // index block of this vector, relative to the tile
-    const int d_off = (lb * d_chunk + q % g.qs_l) * 4;
-    const int d_stride = g.qs_l * 4;
-    const int a_off = (wm * WM + lm * (MT >= 4 ? 4 : 2)) * 4;
-    const int b_off = (vec * kVecLen + (lane >> 4) * 8 + (lane & 1) * 4) * 4;
-
-    // The warps take turns refilling the ring: at the top of iteration `it`, warp
-    // it % NCW loads window it+STAGES-1 into the stage that window it-1 has left, so
-    // STAGES-1 windows are in flight while window `it` is multiplied.
-    for (int it = 0; it < nwin; ++it) {
-        const int s = it % STAGES;
-        const int nxt = it + STAGES - 1;
-#ifdef NMSPMM_FFMA_WINDOW_SYNC
-        __syncthreads();
+#ifdef NMSPMM_PROFILE_WAITS
+    long long prof_wait = 0, prof_fill = 0;
+    const long long prof_start = clock64();
 #endif
-        if (nxt < nwin && it % NCW == warp) {
-            if (!fill(nxt)) break;
-        }
-        const bool ok = mbar_wait_bounded(smem_u32(&bars[s]), (it / STAGES) & 1, abort_flag);
-        if (!__all_sync(0xffffffffu, ok)) {                // the whole warp gives up together
-            if (lane == 0) atomicMax(g.status, kDevTimeoutFull);
-            break;
-        }
-        if (live) {
-            const unsigned char* st = ring + s * Cfg::STAGE_BYTES;
-            const unsigned char* as = st + a_off;
-            const unsigned char* bs = st + Cfg::A_BYTES + b_off;
-            const unsigned char* ds = st + Cfg::A_BYTES + Cfg::B_BYTES + d_off;
+    int s = 0, use = 0;                                    // stage of the window being multiplied, and its use count
+    const uint32_t a_rel = (wm * WM + lm * (MT >= 4 ? 4 : 2)) * 4;
+    const uint32_t b_rel = Cfg::A_BYTES + (vec * kVecLen + (lane >> 4) * 8 + (lane & 1) * 4) * 4;
 
-            int row_off[WS];
-#pragma unroll
-            for (int p = 0; p < WS; ++p) row_off[p] = *reinterpret_cast<const int*>(ds + p * d_stride);
-            if constexpr (MODE == kModeHigh) {             // rank -> local column through the block's list
-                const int* list = reinterpret_cast<const int*>(st + Cfg::A_BYTES + Cfg::B_BYTES + Cfg::D_BYTES) + lb * 64;
-#pragma unroll
-                for (int p = 0; p < WS; ++p) row_off[p] = list[row_off[p]];
-            }
-#pragma unroll
-            for (int p = 0; p < WS; ++p) row_off[p] *= (MS * 4);
+    // One iteration per piece: consecutive windows of one tile.
+    for (int cu = u_begin; cu < u_end;) {
+        const int tile = cu / g.sched.n_win;
+        const int piece_n = min((tile + 1) * g.sched.n_win, u_end) - cu;
+        const int win0 = cu - tile * g.sched.n_win;        // first window of the piece
+        uint32_t d_rel, ci_rel;
+        bool live;
+        {
+            const int ty = tile / g.tiles_x, tx = tile - ty * g.tiles_x;
+            const int bj = tx * NS;
+            live = (vec * kVecLen < g.N - bj);             // vectors past N idle but keep the ring moving
+            const int q = (bj >> 5) + vec;                 // global vector number
+            const int lb = (q >> qs_shift) - (bj >> layout_shift);   // its index block, relative to the tile
+            d_rel = Cfg::A_BYTES + Cfg::B_BYTES + (lb * d_chunk + (lane << qs_shift) + (q & ((1 << qs_shift) - 1))) * 4;
+            ci_rel = Cfg::A_BYTES + Cfg::B_BYTES + Cfg::D_BYTES + lb * 256;
+        }
 
-            float a[2][MT];
-            float4 b[2][2];
-            auto load = [&](int p, int buf) {
-                const unsigned char* ap = as + row_off[p];
-                if constexpr (MT == 8) {
-                    *reinterpret_cast<float4*>(&a[buf][0]) = *reinterpret_cast<const float4*>(ap);
-                    *reinterpret_cast<float4*>(&a[buf][4]) = *reinterpret_cast<const float4*>(ap + 32 * 4);
-                } else if constexpr (MT == 4) {
-                    *reinterpret_cast<float4*>(&a[buf][0]) = *reinterpret_cast<const float4*>(ap);
-                } else {
-                    *reinterpret_cast<float2*>(&a[buf][0]) = *reinterpret_cast<const float2*>(ap);
+        float2 acc[MT][4];                                 // row i, column pairs (0,1) (2,3) | (16,17) (18,19)
+#pragma unroll
+        for (int i = 0; i < MT; ++i)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[i][c] = make_float2(0.0f, 0.0f);
+
+        for (int w = 0; w < piece_n; ++w) {
+            // One CTA barrier per window keeps the warps in step (left alone they drift
+            // apart by the whole depth of the ring and then wait for one another); the
+            // second CTA of the SM computes meanwhile.  After it the previous window's
+            // stage is free: the warps take turns loading the window STAGES-1 ahead into it.
+            __syncthreads();
+            {
+                const int next = cu + w + STAGES - 1;
+                if (next < u_end && ((cu + w) % NCW) == warp) {
+                    if (lane == 0) fence_proxy_async();    // the CTA's reads of the stage come before the TMA's writes
+                    __syncwarp();
+                    NMSPMM_PROF_T(tf);
+                    fill(s == 0 ? STAGES - 1 : s - 1, next);
+                    NMSPMM_PROF_ADD(prof_fill, tf);
                 }
-                const unsigned char* bp = bs + p * (NS * 4);
-                b[buf][0] = *reinterpret_cast<const float4*>(bp);
-                b[buf][1] = *reinterpret_cast<const float4*>(bp + 16 * 4);
-            };
-            load(0, 0);
+            }
+            // A wait that gives up raises the CTA's abort word; every later wait then fails
+            // at once, the warps keep walking the loop for the barriers' sake, and the CTA
+            // leaves together at the end of the piece without storing anything.
+            NMSPMM_PROF_T(tw);
+            const bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(bars + s * 8, use & 1, abort_word));
+            NMSPMM_PROF_ADD(prof_wait, tw);
+            if (live && ok) {
+                // HALF: the list holds columns of the merged 64-k window; the staged rows are
+                // its lower (even window) or upper (odd window) 32
+                const int half_base = Cfg::HALF ? (((win0 + w) & 1) << 5) : 0;
+                const uint32_t st = ring + s * Cfg::STAGE_BYTES;
+                const uint32_t as = st + a_rel, bs = st + b_rel;
+
+#ifndef NMSPMM_IDX_SHFL
+#define NMSPMM_IDX_SHFL 1
+#endif
+#ifndef NMSPMM_ASM_LDS
+#define NMSPMM_ASM_LDS 1
+#endif
+#if NMSPMM_IDX_SHFL
+                // Lane p resolves the window's p-th index of this warp's vector to a byte
+                // offset into As (HIGH: rank -> local column through the block's list); the
+                // offsets are handed round the warp by shuffle as the k loop needs them.
+                int my_off = 0;
+                if (lane < WS) {
+                    int k = lds_s32(st + d_rel);
+                    if constexpr (MODE == kModeHigh) k = lds_s32(st + ci_rel + k * 4) - half_base;
+                    my_off = k * (MS * 4);
+                }
+#define NMSPMM_OFF(p) __shfl_sync(0xffffffffu, my_off, (p))
+#else
+                int row_off[WS];
 #pragma unroll
-            for (int p = 0; p < WS; ++p) {
-                if (p + 1 < WS) load(p + 1, (p + 1) & 1);
-                // Packed FP32 FMA (two lanes per instruction): the B pairs come straight
-                // out of the 128-bit loads, the A value is duplicated into a pair.  Each
-                // component rounds exactly like a scalar fmaf.
-                const float4 b0 = b[p & 1][0], b1 = b[p & 1][1];
-                const float2 bp0 = make_float2(b0.x, b0.y), bp1 = make_float2(b0.z, b0.w);
-                const float2 bp2 = make_float2(b1.x, b1.y), bp3 = make_float2(b1.z, b1.w);
+                for (int p = 0; p < WS; ++p) row_off[p] = lds_s32(st + d_rel - (lane << (qs_shift + 2)) + ((p << qs_shift) << 2));
+                if constexpr (MODE == kModeHigh) {
 #pragma unroll
-                for (int i = 0; i < MT; ++i) {
-                    const float2 aa = make_float2(a[p & 1][i], a[p & 1][i]);
-                    if (i & 1) {                                   // serpentine over the column pairs
-                        acc[i][3] = __ffma2_rn(aa, bp3, acc[i][3]);
-                        acc[i][2] = __ffma2_rn(aa, bp2, acc[i][2]);
-                        acc[i][1] = __ffma2_rn(aa, bp1, acc[i][1]);
-                        acc[i][0] = __ffma2_rn(aa, bp0, acc[i][0]);
+                    for (int p = 0; p < WS; ++p) row_off[p] = lds_s32(st + ci_rel + row_off[p] * 4) - half_base;
+                }
+#pragma unroll
+                for (int p = 0; p < WS; ++p) row_off[p] *= (MS * 4);
+#define NMSPMM_OFF(p) row_off[(p)]
+#endif
+
+                float a[2][MT];
+                float4 b[2][2];
+                auto load = [&](int p, int buf, int off) {
+                    const uint32_t ap = as + off;
+#if NMSPMM_ASM_LDS
+                    if constexpr (MT == 8) {
+                        const float4 lo = lds_f4(ap), hi = lds_f4(ap + 32 * 4);
+                        a[buf][0] = lo.x; a[buf][1] = lo.y; a[buf][2] = lo.z; a[buf][3] = lo.w;
+                        a[buf][4] = hi.x; a[buf][5] = hi.y; a[buf][6] = hi.z; a[buf][7] = hi.w;
+                    } else if constexpr (MT == 4) {
+                        const float4 lo = lds_f4(ap);
+                        a[buf][0] = lo.x; a[buf][1] = lo.y; a[buf][2] = lo.z; a[buf][3] = lo.w;
                     } else {
-                        acc[i][0] = __ffma2_rn(aa, bp0, acc[i][0]);
-                        acc[i][1] = __ffma2_rn(aa, bp1, acc[i][1]);
-                        acc[i][2] = __ffma2_rn(aa, bp2, acc[i][2]);
-                        acc[i][3] = __ffma2_rn(aa, bp3, acc[i][3]);
+                        const float2 lo = lds_f2(ap);
+                        a[buf][0] = lo.x; a[buf][1] = lo.y;
+                    }
+                    const uint32_t bp = bs + p * (NS * 4);
+                    b[buf][0] = lds_f4(bp);
+                    b[buf][1] = lds_f4(bp + 16 * 4);
+#else
+                    const unsigned char* base = smem_raw - smem_u32(smem_raw);      // shared window origin
+                    if constexpr (MT == 8) {
+                        *reinterpret_cast<float4*>(&a[buf][0]) = *reinterpret_cast<const float4*>(base + ap);
+                        *reinterpret_cast<float4*>(&a[buf][4]) = *reinterpret_cast<const float4*>(base + ap + 32 * 4);
+                    } else if constexpr (MT == 4) {
+                        *reinterpret_cast<float4*>(&a[buf][0]) = *reinterpret_cast<const float4*>(base + ap);
+                    } else {
+                        *reinterpret_cast<float2*>(&a[buf][0]) = *reinterpret_cast<const float2*>(base + ap);
+                    }
+                    const uint32_t bp = bs + p * (NS * 4);
+                    b[buf][0] = *reinterpret_cast<const float4*>(base + bp);
+                    b[buf][1] = *reinterpret_cast<const float4*>(base + bp + 16 * 4);
+#endif
+                };
+                load(0, 0, NMSPMM_OFF(0));
+                int off_next = (WS > 1) ? NMSPMM_OFF(1) : 0;
+#pragma unroll
+                for (int p = 0; p < WS; ++p) {
+                    if (p + 1 < WS) {
+                        load(p + 1, (p + 1) & 1, off_next);
+                        if (p + 2 < WS) off_next = NMSPMM_OFF(p + 2);
+                    }
+                    // Packed FP32 FMA (two lanes per instruction): the B pairs come straight
+                    // out of the 128-bit loads, the A value is duplicated into a pair.  Each
+                    // component rounds exactly like a scalar fmaf.
+                    const float4 b0 = b[p & 1][0], b1 = b[p & 1][1];
+                    const float2 bp0 = make_float2(b0.x, b0.y), bp1 = make_float2(b0.z, b0.w);
+                    const float2 bp2 = make_float2(b1.x, b1.y), bp3 = make_float2(b1.z, b1.w);
+#pragma unroll
+                    for (int i = 0; i < MT; ++i) {
+                        const float2 aa = make_float2(a[p & 1][i], a[p & 1][i]);
+                        if (i & 1) {                               // serpentine over the column pairs
+                            acc[i][3] = __ffma2_rn(aa, bp3, acc[i][3]);
+                            acc[i][2] = __ffma2_rn(aa, bp2, acc[i][2]);
+                            acc[i][1] = __ffma2_rn(aa, bp1, acc[i][1]);
+                            acc[i][0] = __ffma2_rn(aa, bp0, acc[i][0]);
+                        } else {
+                            acc[i][0] = __ffma2_rn(aa, bp0, acc[i][0]);
+                            acc[i][1] = __ffma2_rn(aa, bp1, acc[i][1]);
+                            acc[i][2] = __ffma2_rn(aa, bp2, acc[i][2]);
+                            acc[i][3] = __ffma2_rn(aa, bp3, acc[i][3]);
+                        }
                     }
                 }
             }
+            __syncwarp();
+            if (++s == STAGES) { s = 0; ++use; }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bars[STAGES + s]));
-    }
+        __syncthreads();
+        if (lds_volatile_s32(abort_word) != 0) {           // a bounded wait gave up somewhere in the CTA
+            if (tid == 0) atomicMax(g.status, kDevTimeoutFull);
+            break;
+        }
 
-    // ---------------------------------------------------------------- epilogue
-    const bool aborted = (*abort_flag != 0);
-    const int col0 = bj + vec * kVecLen + (lane >> 4) * 8 + (lane & 1) * 4;      // and col0 + 16
-    const bool store = live && !aborted;
-    auto row_of = [&](int i) {
-        return bi + wm * WM + ((MT == 8) ? ((i < 4) ? lm * 4 + i : 32 + lm * 4 + (i - 4))
-                                         : ((MT == 4) ? lm * 4 + i : lm * 2 + i));
-    };
-
-    if (g.split_k == 1) {
-        if (store) {
+        // ---------------------------------------------------------------- end of the piece
+        const int ty = tile / g.tiles_x, tx = tile - ty * g.tiles_x;
+        const int bj = tx * NS, bi = ty * MS;
+        const int col0 = bj + vec * kVecLen + (lane >> 4) * 8 + (lane & 1) * 4;      // and col0 + 16
+        auto row_of = [&](int i) {
+            return bi + wm * WM + ((MT == 8) ? ((i < 4) ? lm * 4 + i : 32 + lm * 4 + (i - 4))
+                                             : ((MT == 4) ? lm * 4 + i : lm * 2 + i));
+        };
+        auto store_tile = [&]() {
+            if (!live) return;
 #pragma unroll
             for (int i = 0; i < MT; ++i) {
                 const int r = row_of(i);
@@ -258,64 +343,79 @@ nm_gemm_ffma_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
                     *reinterpret_cast<float4*>(cp + 16) = make_float4(acc[i][2].x, acc[i][2].y, acc[i][3].x, acc[i][3].y);
                 }
             }
+        };
+        if (piece_n == g.sched.n_win) {
+            store_tile();                                  // the whole tile was computed here
+        } else {
+            // A piece of the tile: park it in this range's scratch slot; the last piece to
+            // arrive adds all pieces in k order and writes C.
+            int v_first, v_last;
+            tile_contributors(g.sched, tile, v_first, v_last);
+            auto slot_of = [&](int v) -> size_t { return static_cast<size_t>(piece_slot(g.sched, v, tile)); };
+            float4* slots = reinterpret_cast<float4*>(g.partial);
+            constexpr size_t kSlot = static_cast<size_t>(E) * NCT;             // float4 words per slot
+            {
+                float4* mine = slots + slot_of(blockIdx.x) * kSlot + tid;
+#pragma unroll
+                for (int i = 0; i < MT; ++i) {
+                    __stcg(mine + (2 * i) * NCT, make_float4(acc[i][0].x, acc[i][0].y, acc[i][1].x, acc[i][1].y));
+                    __stcg(mine + (2 * i + 1) * NCT, make_float4(acc[i][2].x, acc[i][2].y, acc[i][3].x, acc[i][3].y));
+                }
+            }
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) {
+                const unsigned n_pieces = static_cast<unsigned>(v_last - v_first + 1);
+                const unsigned prev = atomicAdd(&g.counters[tile], 1u);
+                const bool last = (prev == n_pieces - 1u);
+                if (last) g.counters[tile] = 0u;               // ready for the next call
+                sts_volatile_s32(last_word, last ? 1 : 0);
+            }
+            __syncthreads();
+            const bool last = (lds_volatile_s32(last_word) != 0);
+            if (last) {
+                __threadfence();
+                if (live) {
+                    // the accumulators are free again: gather the pieces into them
+#pragma unroll
+                    for (int i = 0; i < MT; ++i)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) acc[i][c] = make_float2(0.0f, 0.0f);
+                    for (int v = v_first; v <= v_last; ++v) {          // fixed order: ascending k
+                        const float4* src = slots + slot_of(v) * kSlot + tid;
+#pragma unroll
+                        for (int i = 0; i < MT; ++i) {
+                            const float4 x = __ldcg(src + (2 * i) * NCT), y = __ldcg(src + (2 * i + 1) * NCT);
+                            acc[i][0].x += x.x; acc[i][0].y += x.y; acc[i][1].x += x.z; acc[i][1].y += x.w;
+                            acc[i][2].x += y.x; acc[i][2].y += y.y; acc[i][3].x += y.z; acc[i][3].y += y.w;
+                        }
+                    }
+                    store_tile();
+                }
+            }
+            __syncthreads();                               // last_flag is reused by the next piece
         }
-        return;
-    }
 
-    const size_t tile = static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x;
-    constexpr int E = MT * 2;                              // float4 words per thread
-    float4* part = reinterpret_cast<float4*>(g.partial) + (tile * g.split_k) * (static_cast<size_t>(E) * NCT);
-    if (!aborted) {
-        float4* mine = part + static_cast<size_t>(z) * E * NCT + tid;
-#pragma unroll
-        for (int i = 0; i < MT; ++i) {
-            __stcg(mine + (2 * i) * NCT, make_float4(acc[i][0].x, acc[i][0].y, acc[i][1].x, acc[i][1].y));
-            __stcg(mine + (2 * i + 1) * NCT, make_float4(acc[i][2].x, acc[i][2].y, acc[i][3].x, acc[i][3].y));
-        }
+        cu += piece_n;                                     // on to the next piece of the range
     }
-    __threadfence();
-    __syncthreads();
+#ifdef NMSPMM_PROFILE_WAITS
     if (tid == 0) {
-        const unsigned prev = atomicAdd(&g.counters[tile], 1u);
-        if (prev == static_cast<unsigned>(g.split_k) - 1u) {
-            *last_flag = 1;
-            g.counters[tile] = 0u;                         // ready for the next call
-        }
+        atomicAdd(&g_wait_profile[0], static_cast<unsigned long long>(prof_wait));
+        atomicAdd(&g_wait_profile[1], static_cast<unsigned long long>(prof_fill));
+        atomicAdd(&g_wait_profile[2], static_cast<unsigned long long>(clock64() - prof_start));
+        atomicAdd(&g_wait_profile[3], 1ull);
     }
-    __syncthreads();
-    if (*last_flag == 0) return;
-    __threadfence();
-    if (!store) return;
-    float4 sum[E];
-#pragma unroll
-    for (int e = 0; e < E; ++e) sum[e] = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s = 0; s < g.split_k; ++s) {                  // fixed order: slice 0, 1, ...
-        const float4* src = part + static_cast<size_t>(s) * E * NCT + tid;
-#pragma unroll
-        for (int e = 0; e < E; ++e) {
-            const float4 v = __ldcg(src + e * NCT);
-            sum[e].x += v.x; sum[e].y += v.y; sum[e].z += v.z; sum[e].w += v.w;
-        }
-    }
-#pragma unroll
-    for (int i = 0; i < MT; ++i) {
-        const int r = row_of(i);
-        if (r < g.M) {
-            float* cp = g.C + static_cast<size_t>(r) * g.N + col0;
-            *reinterpret_cast<float4*>(cp) = sum[2 * i];
-            *reinterpret_cast<float4*>(cp + 16) = sum[2 * i + 1];
-        }
-    }
+#endif
 }
 
 // Host-side launcher of one variant: encodes the two tensor maps (A as [K][M] with an
 // MS x KS box, B as [W][N] with an NS x WS box) and sets the dynamic shared-memory
 // limit once per device.
-template <int MS, int NS, int WM, int WS, int MODE>
-cudaError_t launch_ffma(const GemmArgs& a, dim3 grid, cudaStream_t st)
+template <int MS, int NS, int WM, int WS, int KS_, int MODE>
+cudaError_t launch_ffma(const GemmArgs& a, int grid, cudaStream_t st)
 {
-    using Cfg = FfmaCfg<MS, NS, WM, WS, MODE>;
-    auto kernel = nm_gemm_ffma_kernel<MS, NS, WM, WS, MODE>;
+    using Cfg = FfmaCfg<MS, NS, WM, WS, KS_, MODE>;
+    auto kernel = nm_gemm_ffma_kernel<MS, NS, WM, WS, KS_, MODE>;
     static bool configured[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -326,7 +426,7 @@ cudaError_t launch_ffma(const GemmArgs& a, dim3 grid, cudaStream_t st)
         configured[dev] = true;
     }
     CUtensorMap map_a, map_b;
-    e = encode_tensor_map_2d(&map_a, a.A, a.M, a.n_win * Cfg::KS, MS, Cfg::KS);
+    e = encode_tensor_map_2d(&map_a, a.A, a.M, a.sched.n_win * Cfg::KS, MS, Cfg::KS);
     if (e != cudaSuccess) return e;
     e = encode_tensor_map_2d(&map_b, a.B, a.N, a.W, NS, WS);
     if (e != cudaSuccess) return e;
@@ -334,17 +434,17 @@ cudaError_t launch_ffma(const GemmArgs& a, dim3 grid, cudaStream_t st)
     return cudaGetLastError();
 }
 
-#define NMSPMM_FFMA_VARIANT(ID, MS, NS, WM, WS, MODE)                                                   \
-    FfmaVariant { ID, MS, NS, WS, MODE, FfmaCfg<MS, NS, WM, WS, MODE>::THREADS,                          \
-                  FfmaCfg<MS, NS, WM, WS, MODE>::SMEM_BYTES, FfmaCfg<MS, NS, WM, WS, MODE>::STAGES,      \
-                  FfmaCfg<MS, NS, WM, WS, MODE>::MIN_BLOCKS, &launch_ffma<MS, NS, WM, WS, MODE> }
+#define NMSPMM_FFMA_VARIANT(ID, NKEEP, MS, NS, WM, WS, KS, MODE)                                            \
+    FfmaVariant { ID, MS, NS, NKEEP, WS, KS, MODE, FfmaCfg<MS, NS, WM, WS, KS, MODE>::THREADS,               \
+                  FfmaCfg<MS, NS, WM, WS, KS, MODE>::SMEM_BYTES, FfmaCfg<MS, NS, WM, WS, KS, MODE>::STAGES,  \
+                  FfmaCfg<MS, NS, WM, WS, KS, MODE>::MIN_BLOCKS, &launch_ffma<MS, NS, WM, WS, KS, MODE> }
 
-// All tiles for one (WS, MODE).
-#define NMSPMM_FFMA_TILES(WS, MODE)                          \
-    NMSPMM_FFMA_VARIANT(kTile128x128, 128, 128, 64, WS, MODE), \
-    NMSPMM_FFMA_VARIANT(kTile64x128, 64, 128, 64, WS, MODE),   \
-    NMSPMM_FFMA_VARIANT(kTile32x128, 32, 128, 32, WS, MODE),   \
-    NMSPMM_FFMA_VARIANT(kTile16x128, 16, 128, 16, WS, MODE),   \
-    NMSPMM_FFMA_VARIANT(kTile128x256, 128, 256, 64, WS, MODE)
+// All tiles for one (kept rows per 32-window, B rows per stage, A rows per stage, MODE).
+#define NMSPMM_FFMA_TILES(NKEEP, WS, KS, MODE)                            \
+    NMSPMM_FFMA_VARIANT(kTile128x128, NKEEP, 128, 128, 64, WS, KS, MODE), \
+    NMSPMM_FFMA_VARIANT(kTile64x128, NKEEP, 64, 128, 64, WS, KS, MODE),   \
+    NMSPMM_FFMA_VARIANT(kTile32x128, NKEEP, 32, 128, 32, WS, KS, MODE),   \
+    NMSPMM_FFMA_VARIANT(kTile16x128, NKEEP, 16, 128, 16, WS, KS, MODE),   \
+    NMSPMM_FFMA_VARIANT(kTile128x256, NKEEP, 128, 256, 64, WS, KS, MODE)
 
 }  // namespace nmspmm

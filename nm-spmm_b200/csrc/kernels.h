@@ -15,13 +15,15 @@ cudaError_t launch_preprocess_high(const int* DT, int* D, int* cinfo, int pm, in
 struct FfmaVariant {
     int tile_id;        // nmspmm_tile
     int ms, ns;         // CTA tile
-    int ws;             // compressed rows per window
+    int n_keep;         // kept rows per 32-k window this variant is compiled for
+    int ws;             // compressed rows of B per staged window
+    int ks;             // rows of A per staged window (32, or 64: a merged HIGH window)
     int mode;           // kModeLow / kModeHigh
     int threads, smem_bytes, stages, min_blocks;
-    cudaError_t (*launch)(const GemmArgs&, dim3 grid, cudaStream_t st);
+    cudaError_t (*launch)(const GemmArgs&, int grid, cudaStream_t st);
 };
 // Returns nullptr when the combination was not compiled.
-const FfmaVariant* find_ffma_variant(int tile_id, int ws, int mode);
+const FfmaVariant* find_ffma_variant(int tile_id, int n_keep, int mode);
 
 // Row-major 2-D float tensor [rows][cols] (cols innermost) with a box_cols x box_rows box, no swizzle;
 // elements outside the tensor are delivered as zeros.

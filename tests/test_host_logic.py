@@ -42,44 +42,77 @@ def test_status_strings(pkg):
 
 
 @pytest.mark.parametrize("M,N,K,n_keep,fmt,Ns,expect_tile", [
-    (4096, 4096, 4096, 16, 0, 128, (128, 256)),
-    (4096, 4096, 4096, 8, 1, 128, (128, 256)),
-    (1024, 1024, 4096, 8, 1, 128, (128, 128)),
+    (4096, 4096, 4096, 16, 0, 128, (128, 128)),
+    (4096, 4096, 4096, 8, 1, 128, (128, 128)),
     (16, 11008, 4096, 8, 1, 128, (16, 128)),
     (64, 11008, 4096, 8, 1, 128, (64, 128)),
     (256, 11008, 4096, 8, 1, 128, (128, 128)),
     (192, 1024, 1024, 16, 0, 64, (64, 128)),
-    (4096, 4096, 4096, 4, 1, 64, (128, 256)),
-    (8192, 28672, 8192, 8, 1, 32, (128, 256)),
+    (8192, 28672, 8192, 8, 1, 32, (128, 128)),
 ])
 def test_plan_selection(pkg, M, N, K, n_keep, fmt, Ns, expect_tile):
-    info = pkg.plan(pkg.make_desc(M, N, K, n_keep, fmt, Ns))
+    d = pkg.make_desc(M, N, K, n_keep, fmt, Ns)
+    info = pkg.plan(d)
     assert (info.tile_m, info.tile_n) == expect_tile
-    assert info.grid_x == -(-N // info.tile_n) and info.grid_y == -(-M // info.tile_m)
+    assert info.tiles_x == -(-N // info.tile_n) and info.tiles_y == -(-M // info.tile_m)
     ws = n_keep if fmt == 0 else 2 * n_keep
     n_win = K // 32 * n_keep // ws
-    assert 1 <= info.split_k <= n_win and info.grid_z == info.split_k
+    tiles = info.tiles_x * info.tiles_y
+    assert info.stream_k == 1 and 1 <= info.n_virtual <= tiles * n_win
+    assert info.grid == info.n_virtual and 0 <= info.n_dp <= tiles
     assert info.stages >= 2 and info.smem_bytes <= 227 * 1024
-    d = pkg.make_desc(M, N, K, n_keep, fmt, Ns)
     need = pkg.workspace_bytes(d)
-    if info.split_k == 1:
-        assert need == 0
-    else:
-        tiles = info.grid_x * info.grid_y
-        assert need >= tiles * info.split_k * info.tile_m * info.tile_n * 4
+    assert need == 0 or need >= 2 * (info.n_virtual - info.n_dp) * info.tile_m * info.tile_n * 4
+
+
+def _ranges(n_tiles, n_win, nv, n_dp):
+    """Host restatement of the automatic unit schedule (virtual_range in gemm_args.h)."""
+    out = [(v * n_win, (v + 1) * n_win) for v in range(n_dp)]
+    base, total, n_sk = n_dp * n_win, (n_tiles - n_dp) * n_win, nv - n_dp
+    out += [(base + i * total // n_sk, base + (i + 1) * total // n_sk) for i in range(n_sk)]
+    return out
+
+
+@pytest.mark.parametrize("n_tiles,n_win,nv,n_dp", [(1024, 64, 888 + 296, 888), (86, 64, 592, 0), (8, 2048, 296, 0),
+                                                   (3, 5, 7, 0), (5, 1, 5, 0), (7, 3, 21, 0), (10, 4, 6 + 5, 6)])
+def test_automatic_schedule_covers_every_unit_once(n_tiles, n_win, nv, n_dp):
+    r = _ranges(n_tiles, n_win, nv, n_dp)
+    assert r[0][0] == 0 and r[-1][1] == n_tiles * n_win and all(a[1] == b[0] for a, b in zip(r, r[1:]))
+    total, n_sk = (n_tiles - n_dp) * n_win, nv - n_dp
+    for t in range(n_tiles):
+        holders = [v for v, (a, b) in enumerate(r) if a <= t * n_win + n_win - 1 and b > t * n_win]
+        if t < n_dp:
+            assert holders == [t]
+        else:                                                   # tile_contributors() in gemm_args.h
+            x0, x1 = (t - n_dp) * n_win, (t - n_dp) * n_win + n_win - 1
+            v_first, v_last = n_dp + ((x0 + 1) * n_sk - 1) // total, n_dp + ((x1 + 1) * n_sk - 1) // total
+            assert holders == list(range(v_first, v_last + 1))
+
+
+def test_plan_balances_the_last_wave(pkg):
+    info = pkg.plan(pkg.make_desc(2048, 3072, 4096, 8, 1, 128))               # 384 tiles: one full wave of 296 + 88
+    tiles = info.tiles_x * info.tiles_y
+    assert info.stream_k == 1 and 0 < info.n_dp < tiles and info.n_dp % (info.n_virtual - info.n_dp) == 0
+    many = pkg.plan(pkg.make_desc(4096, 4096, 4096, 8, 1, 128))               # 1024 tiles: whole tiles only
+    assert many.n_dp == many.n_virtual == 1024
+    exact = pkg.plan(pkg.make_desc(128 * 296 // 8, 1024, 4096, 8, 1, 128))      # 37 x 8 = 296 tiles: nothing to balance
+    assert exact.n_dp == exact.tiles_x * exact.tiles_y == exact.n_virtual
+    assert pkg.workspace_bytes(pkg.make_desc(128 * 296 // 8, 1024, 4096, 8, 1, 128)) == 0
 
 
 def test_split_k_fills_the_machine_for_skinny_shapes(pkg):
     big = pkg.plan(pkg.make_desc(4096, 4096, 4096, 8, 1, 128))
-    assert big.split_k == 1
+    assert big.split_k == 1 and big.grid == big.n_virtual
     skinny = pkg.plan(pkg.make_desc(16, 11008, 4096, 8, 1, 128))
-    assert skinny.split_k > 1
+    assert skinny.split_k > 1 and skinny.n_virtual > 86
     deep = pkg.plan(pkg.make_desc(128, 1024, 131072, 4, 1, 128))
     assert deep.split_k >= 16
     forced = pkg.plan(pkg.make_desc(128, 1024, 131072, 4, 1, 128, split_k=7))
-    assert forced.split_k == 7
+    assert forced.split_k == 7 and forced.stream_k == 0 and forced.n_virtual == 8 * 7
     clamped = pkg.plan(pkg.make_desc(128, 128, 64, 16, 0, 128, split_k=9))
     assert clamped.split_k == 2            # only two windows exist
+    one = pkg.plan(pkg.make_desc(128, 128, 64, 16, 0, 128, split_k=1))
+    assert one.split_k == 1 and pkg.workspace_bytes(pkg.make_desc(128, 128, 64, 16, 0, 128, split_k=1)) == 0
 
 
 @pytest.mark.parametrize("kw,status", [
