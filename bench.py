@@ -43,9 +43,10 @@ HEADLINE_KEEP = 8
 SETS = 3                      # operand sets rotated between steps (3 x 144 MB > 126 MB of L2)
 METRIC = "useful TFLOP/s, vector-wise N:M SpMM, 4096^3 8:32 V=32 FP32"
 
-# DRAM bytes per launch of the headline kernel from the ncu capture summarised in
-# profiles/ (null until a capture exists for the exact kernel and workload).
-NCU_TRAFFIC_BYTES = {"nm_gemm_ffma_kernel<128,128,64,16,high> 4096^3 8:32": None}
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the headline
+# kernel, from the ncu capture summarised in
+# profiles/nm_gemm_ffma_128x128_high_4096cubed_8of32.md.
+NCU_TRAFFIC_BYTES = {"nm_gemm_ffma_kernel<128,128,64,16,64,high> 4096^3 8:32": 127294976}
 
 
 def algorithmic_bytes(M, N, K, n_keep, layout_ns=128):
@@ -305,15 +306,16 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     roofline = {
         "bound": "fp32_simt" if t_flop >= t_mem else "hbm",
         "achieved": achieved, "peak": ffma_peak, "unit": "TFLOP/s", "frac": max(t_flop, t_mem) / (ms_per_step * 1e-3),
-        "traffic": NCU_TRAFFIC_BYTES.get("nm_gemm_ffma_kernel<128,128,64,16,high> 4096^3 8:32"),
+        "traffic": NCU_TRAFFIC_BYTES.get("nm_gemm_ffma_kernel<128,128,64,16,64,high> 4096^3 8:32"),
         "peak_source": "FP32 FMA rate measured live on this GPU by the library's register-only kernels, larger of "
                        f"scalar FFMA ({ffma_scalar:.1f}) and packed FFMA2 ({ffma_packed:.1f} TFLOP/s); "
                        "nominal 148 SMs x 128 lanes x 2 x SM clock",
         "algorithmic_bytes": abytes, "algorithmic_flops": useful,
         "hbm_time_us": t_mem * 1e6, "hbm_peak_gbs": hbm_gbs, "hbm_peak_source": hbm_src,
         "kernel": f"nm_gemm_ffma_kernel tile {plan.tile_m}x{plan.tile_n}, "
-                  f"{'stream-K' if plan.stream_k else 'split_k ' + str(plan.split_k)}: {plan.tiles_x * plan.tiles_y} tiles in "
-                  f"{plan.n_virtual} ranges on {plan.grid} resident CTAs, {plan.stages} stages, {plan.smem_bytes} B smem",
+                  f"{'automatic schedule' if plan.stream_k else 'split_k ' + str(plan.split_k)}: "
+                  f"{plan.tiles_x * plan.tiles_y} tiles ({plan.n_dp} whole) in {plan.n_virtual} unit ranges = CTAs, "
+                  f"{plan.stages} stages, {plan.smem_bytes} B smem",
         "kernel_ms": ms_per_step,
     }
 
