@@ -125,6 +125,32 @@ int nmspmm_gemm_with_cached_workspace(const nmspmm_gemm_desc* desc,
                                       const float* A_dev, const float* B_dev, const int* D_dev,
                                       const int* column_info_dev, float* C_dev, void* stream);
 
+/* The multiply for callers that must not allocate.  (No counterpart in the reference:
+ * its launchers need no scratch because they add split-K partials onto C with atomics.)
+ *
+ * Some hosts of this library cannot call cudaMalloc where the multiply runs: code that
+ * executes inside another framework's allocator discipline, a latency-critical
+ * section where an allocation would synchronise the device, or a process whose memory
+ * budget was handed out in full at start-up.  For them the scratch that nmspmm_gemm
+ * takes from the caller sits in a fixed array inside the library image:
+ * NMSPMM_STATIC_SCRATCH_BYTES bytes of device memory on every GPU that loads the library,
+ * held until the process exits.  The call is nmspmm_gemm with that array as workspace; it
+ * calls no cudaMalloc, cudaFree or other allocating routine.
+ *
+ *  - Descriptions whose nmspmm_gemm_workspace_bytes exceeds NMSPMM_STATIC_SCRATCH_BYTES are
+ *    rejected with NMSPMM_WORKSPACE_TOO_SMALL and a message on stderr (nothing is launched);
+ *    an explicit, smaller split_k lowers the need.
+ *  - The first call on a device looks the array's address up (cudaGetSymbolAddress, with
+ *    that device current) and keeps it; make that first call before any stream capture.
+ *  - Every call uses the same array and it keeps the previous call's contents.  The
+ *    arrival counters at its head are cleared on `stream` ahead of the kernel; the slots
+ *    are written before they are read.  Two calls that overlap on the GPU (different
+ *    streams, or different host threads) race on it: serialise them. */
+#define NMSPMM_STATIC_SCRATCH_BYTES (16u << 20)
+int nmspmm_gemm_static_scratch(const nmspmm_gemm_desc* desc,
+                               const float* A_dev, const float* B_dev, const int* D_dev,
+                               const int* column_info_dev, float* C_dev, void* stream);
+
 /* Reads the device status word that kernels raise when a bounded wait gives up
  * (synchronises the device).  Returns NMSPMM_OK or NMSPMM_DEVICE_TIMEOUT; the raw
  * word goes to *status_out when non-NULL; clear != 0 resets it. */

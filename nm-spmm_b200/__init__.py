@@ -36,7 +36,9 @@ C_ABI_SYMBOLS = (
     "nmspmm_trans_index_host", "nmspmm_preprocess_low_host", "nmspmm_preprocess_high_host",
     "nmspmm_gemm_workspace_bytes", "nmspmm_gemm", "nmspmm_gemm_with_cached_workspace", "nmspmm_device_status",
     "nmspmm_gemm_plan", "nmspmm_gemm_host", "nmspmm_release_cached", "nmspmm_measure_ffma_peak",
+    "nmspmm_gemm_static_scratch",
 )
+STATIC_SCRATCH_BYTES = 16 << 20     # NMSPMM_STATIC_SCRATCH_BYTES of include/nmspmm_b200.h
 
 
 class GemmDesc(ctypes.Structure):
@@ -86,6 +88,7 @@ def load_library():
     lib.nmspmm_gemm_workspace_bytes.argtypes = [ctypes.POINTER(GemmDesc)]
     lib.nmspmm_gemm.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp, vp, sz, vp]
     lib.nmspmm_gemm_with_cached_workspace.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp, vp]
+    lib.nmspmm_gemm_static_scratch.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp, vp]
     lib.nmspmm_device_status.argtypes = [ctypes.POINTER(ci), ci]
     lib.nmspmm_gemm_plan.argtypes = [ctypes.POINTER(GemmDesc), ctypes.POINTER(PlanInfo)]
     lib.nmspmm_gemm_host.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp]
@@ -232,6 +235,18 @@ def gemm(desc: GemmDesc, A, B, D, column_info, C, workspace=None, stream=None) -
            load_library().nmspmm_gemm(ctypes.byref(desc), _dev_ptr(A, torch.float32, "A"), _dev_ptr(B, torch.float32, "B"),
                                       _dev_ptr(D, torch.int32, "D"), ci, _dev_ptr(C, torch.float32, "C"),
                                       ws_ptr, ws_bytes, _stream_ptr(stream)))
+
+
+def gemm_static_scratch(desc: GemmDesc, A, B, D, column_info, C, stream=None) -> None:
+    """nmspmm_gemm_static_scratch on CUDA tensors: the multiply with the library's built-in
+    scratch array instead of a caller workspace, for callers that may not allocate.  Calls
+    that overlap on the GPU race on that array; sizes beyond STATIC_SCRATCH_BYTES raise."""
+    torch = _torch()
+    ci = ctypes.c_void_p(0) if column_info is None else _dev_ptr(column_info, torch.int32, "column_info")
+    _check("nmspmm_gemm_static_scratch",
+           load_library().nmspmm_gemm_static_scratch(
+               ctypes.byref(desc), _dev_ptr(A, torch.float32, "A"), _dev_ptr(B, torch.float32, "B"),
+               _dev_ptr(D, torch.int32, "D"), ci, _dev_ptr(C, torch.float32, "C"), _stream_ptr(stream)))
 
 
 def device_status(clear: bool = True) -> int:

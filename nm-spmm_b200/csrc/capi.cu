@@ -475,6 +475,56 @@ int nmspmm_gemm_with_cached_workspace(const nmspmm_gemm_desc* desc, const float*
     return nmspmm_gemm(desc, A_dev, B_dev, D_dev, column_info_dev, C_dev, ws, ws ? tl_scratch.bytes : 0, stream);
 }
 
+// ---- the entry point that allocates nothing --------------------------------------
+// Scratch for split tiles lives in this file-scope device array: every GPU that loads the
+// library carries these bytes until the process exits.  In host code the name below is
+// only a handle for cudaGetSymbolAddress, never a device pointer.
+static __device__ __align__(256) unsigned char g_static_scratch[NMSPMM_STATIC_SCRATCH_BYTES];
+static void* g_static_scratch_ptr[64];      // per device, resolved on the first call there
+static std::mutex g_static_scratch_mutex;
+
+int nmspmm_gemm_static_scratch(const nmspmm_gemm_desc* desc, const float* A_dev, const float* B_dev, const int* D_dev,
+                               const int* column_info_dev, float* C_dev, void* stream)
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (dev < 0 || dev >= 64) return NMSPMM_UNSUPPORTED;
+    const size_t need = nmspmm_gemm_workspace_bytes(desc);
+    if (need > static_cast<size_t>(NMSPMM_STATIC_SCRATCH_BYTES)) {
+        fprintf(stderr,
+                "nmspmm_gemm_static_scratch: this multiply needs %zu bytes of scratch, the built-in array holds %zu; "
+                "pass a smaller split_k or use nmspmm_gemm with caller scratch\n",
+                need, static_cast<size_t>(NMSPMM_STATIC_SCRATCH_BYTES));
+        return NMSPMM_WORKSPACE_TOO_SMALL;
+    }
+    void* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+        if (!g_static_scratch_ptr[dev]) {
+            // once per device, with that device current: the array's address on this GPU
+            void* p = nullptr;
+            e = cudaGetSymbolAddress(&p, g_static_scratch);
+            if (e != cudaSuccess) return cuda_fail(e);
+            g_static_scratch_ptr[dev] = p;
+        }
+        scratch = g_static_scratch_ptr[dev];
+    }
+    if (need > 0) {
+        // the arrival counters at the head of the scratch must read zero; the slots behind
+        // them are fully written before they are read
+        Plan p;
+        DeviceInfo* di = nullptr;
+        int rc = device_info(&di);
+        if (rc != NMSPMM_OK) return rc;
+        rc = make_plan(desc, di->sms, &p);
+        if (rc != NMSPMM_OK) return rc;
+        e = cudaMemsetAsync(scratch, 0, p.counters_bytes, static_cast<cudaStream_t>(stream));
+        if (e != cudaSuccess) return cuda_fail(e);
+    }
+    return nmspmm_gemm(desc, A_dev, B_dev, D_dev, column_info_dev, C_dev, need ? scratch : nullptr, need, stream);
+}
+
 int nmspmm_gemm_host(const nmspmm_gemm_desc* desc, const float* A_host, const float* B_host, const int* DT_host,
                      float* C_host, void* stream)
 {
