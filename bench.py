@@ -259,11 +259,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     for s in range(1, SETS):
         A_sets.append(torch.roll(A_sets[0], s * 131, dims=1).contiguous())
     C_sets = [torch.empty((M, n_local), dtype=torch.float32, device="cuda") for _ in range(SETS)]
-    desc = op.desc(M, tile=args.tile, split_k=args.split_k)
+    path = pkg.PATH_TF32 if (args.kernel_only and args.path == "tf32") else pkg.PATH_FP32
+    desc = op.desc(M, path=path, tile=args.tile, split_k=args.split_k)
     plan = pkg.plan(desc)
 
     def step(i):
-        op.matmul(A_sets[i % SETS], out=C_sets[i % SETS], tile=args.tile, split_k=args.split_k)
+        op.matmul(A_sets[i % SETS], out=C_sets[i % SETS], path=path, tile=args.tile, split_k=args.split_k)
 
     for i in range(max(3, args.warmup)):
         step(i)
@@ -282,7 +283,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if args.kernel_only:
         if rank == 0:
             print(json.dumps({"kernel_only": True, "ffma_peak": [pkg.measure_ffma_peak(False), pkg.measure_ffma_peak(True)],
-                              "n_keep": keep, "ms_per_step": ms_per_step, "useful_tflops": value,
+                              "n_keep": keep, "path": args.path, "ms_per_step": ms_per_step, "useful_tflops": value,
                               "tile": [plan.tile_m, plan.tile_n], "split_k": plan.split_k, "grid": plan.grid, "stages": plan.stages,
                               "clocks": sampler.summary()}), flush=True)
         if world > 1:
@@ -386,6 +387,7 @@ def main():
     ap.add_argument("--kernel-only", action="store_true",
                     help="only the resident-operand steps (profiling runs): no e2e, CPU baseline or ratio sweep")
     ap.add_argument("--n-keep", type=int, default=HEADLINE_KEEP, help="kept rows per 32-window for --kernel-only runs")
+    ap.add_argument("--path", default="fp32", choices=["fp32", "tf32"], help="arithmetic of --kernel-only runs")
     ap.add_argument("--tile", type=int, default=0, help="force a CTA tile id (tuning runs)")
     ap.add_argument("--split-k", type=int, default=0, help="force the number of K slices (tuning runs)")
     args = ap.parse_args()

@@ -79,6 +79,7 @@ static int device_info(DeviceInfo** out)
 // ---- plan -----------------------------------------------------------------------
 struct Plan {
     const FfmaVariant* v = nullptr;
+    const Tf32Variant* tv = nullptr;   // set instead of v on the tensor-core path
     int W = 0, ws = 0, n_win = 0;
     int tiles_x = 0, tiles_y = 0, n_tiles = 0;
     int split_k = 0;        // > 0 explicit slices per tile, 0 automatic
@@ -125,8 +126,25 @@ static int make_plan(const nmspmm_gemm_desc* d, int sms, Plan* p)
     int mode = 0;
     int rc = check_desc(d, &mode);
     if (rc != NMSPMM_OK) return rc;
-    if (d->path != NMSPMM_PATH_FP32) return NMSPMM_UNSUPPORTED;
     if (sms <= 0) sms = 148;
+    if (d->path == NMSPMM_PATH_TF32) {
+        // Tensor-core path: one 128 x 256 tile per CTA over all k windows (split_k is ignored).
+        for (int i = 0; i < kTf32VariantCount; ++i)
+            if (kTf32Variants[i].n_keep == d->n_keep && kTf32Variants[i].mode == mode) p->tv = &kTf32Variants[i];
+        if (!p->tv) return NMSPMM_UNSUPPORTED;
+        p->ws = p->tv->ws;
+        p->W = d->K / 32 * d->n_keep;
+        p->n_win = p->W / p->ws;
+        p->tiles_x = (d->N + 255) / 256;
+        p->tiles_y = (d->M + 127) / 128;
+        const long long nt = static_cast<long long>(p->tiles_x) * p->tiles_y;
+        if (nt >= (1LL << 30)) return NMSPMM_UNSUPPORTED;
+        p->n_tiles = static_cast<int>(nt);
+        p->split_k = 1;
+        p->n_dp = p->n_virtual = p->grid = p->n_tiles;
+        return NMSPMM_OK;
+    }
+    if (d->path != NMSPMM_PATH_FP32) return NMSPMM_UNSUPPORTED;
     const int tile = d->tile ? d->tile : pick_tile(d, sms);
     const FfmaVariant* v = find_ffma_variant(tile, d->n_keep, mode);
     if (!v) return NMSPMM_UNSUPPORTED;
@@ -391,9 +409,9 @@ int nmspmm_gemm_plan(const nmspmm_gemm_desc* desc, nmspmm_gemm_plan_info* out)
     Plan p;
     int rc = make_plan(desc, sm_count(), &p);
     if (rc != NMSPMM_OK) return rc;
-    out->tile = p.v->tile_id;
-    out->tile_m = p.v->ms;
-    out->tile_n = p.v->ns;
+    out->tile = p.v ? p.v->tile_id : 0;
+    out->tile_m = p.v ? p.v->ms : 128;
+    out->tile_n = p.v ? p.v->ns : 256;
     out->split_k = p.split_k > 0 ? p.split_k
                                  : (p.n_tiles > p.n_dp ? (p.n_virtual - p.n_dp + p.n_tiles - p.n_dp - 1) / (p.n_tiles - p.n_dp) : 1);
     out->n_dp = p.n_dp;
@@ -402,9 +420,9 @@ int nmspmm_gemm_plan(const nmspmm_gemm_desc* desc, nmspmm_gemm_plan_info* out)
     out->n_virtual = p.n_virtual;
     out->grid = p.grid;
     out->stream_k = p.split_k > 0 ? 0 : 1;
-    out->threads = p.v->threads;
-    out->smem_bytes = p.v->smem_bytes;
-    out->stages = p.v->stages;
+    out->threads = p.v ? p.v->threads : 320;
+    out->smem_bytes = p.v ? p.v->smem_bytes : p.tv->smem_bytes;
+    out->stages = p.v ? p.v->stages : p.tv->stages;
     return NMSPMM_OK;
 }
 
@@ -443,7 +461,8 @@ int nmspmm_gemm(const nmspmm_gemm_desc* desc, const float* A_dev, const float* B
         a.counters = static_cast<unsigned*>(workspace_dev);
         a.partial = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace_dev) + p.counters_bytes);
     }
-    cudaError_t e = p.v->launch(a, p.grid, static_cast<cudaStream_t>(stream));
+    cudaError_t e = p.v ? p.v->launch(a, p.grid, static_cast<cudaStream_t>(stream))
+                        : p.tv->launch(a, p.grid, static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? NMSPMM_OK : cuda_fail(e);
 }
 

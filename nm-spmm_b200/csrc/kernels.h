@@ -25,9 +25,23 @@ struct FfmaVariant {
 // Returns nullptr when the combination was not compiled.
 const FfmaVariant* find_ffma_variant(int tile_id, int n_keep, int mode);
 
-// Row-major 2-D float tensor [rows][cols] (cols innermost) with a box_cols x box_rows box, no swizzle;
-// elements outside the tensor are delivered as zeros.
-cudaError_t encode_tensor_map_2d(CUtensorMap* map, const float* base, int cols, int rows, int box_cols, int box_rows);
+// Row-major 2-D float tensor [rows][cols] (cols innermost) with a box_cols x box_rows box;
+// swizzle128 = 0: rows land unswizzled, 1: 32-byte chunks swizzled within 128-byte rows
+// (CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B; box_cols * 4 must be 128).
+// Elements outside the tensor are delivered as zeros.
+cudaError_t encode_tensor_map_2d(CUtensorMap* map, const float* base, int cols, int rows, int box_cols, int box_rows,
+                                 int swizzle128 = 0);
+
+// One compiled TF32 tensor-core kernel variant (tile 128 x 256).
+struct Tf32Variant {
+    int n_keep;         // kept rows per 32-k window
+    int ws, ks;         // rows of B / of A per staged window
+    int mode;
+    int smem_bytes, stages;
+    cudaError_t (*launch)(const GemmArgs&, int tiles, cudaStream_t st);
+};
+extern const Tf32Variant kTf32Variants[];
+extern const int kTf32VariantCount;
 
 // packed = 0: scalar FFMA loop; 1: two-lane packed FFMA2 loop.
 cudaError_t measure_ffma_peak(double* tflops, int packed, cudaStream_t st);

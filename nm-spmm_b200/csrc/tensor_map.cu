@@ -25,7 +25,8 @@ static EncodeTiledFn encode_fn()
     return fn;
 }
 
-cudaError_t encode_tensor_map_2d(CUtensorMap* map, const float* base, int cols, int rows, int box_cols, int box_rows)
+cudaError_t encode_tensor_map_2d(CUtensorMap* map, const float* base, int cols, int rows, int box_cols, int box_rows,
+                                 int swizzle128)
 {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return cudaErrorNotSupported;
@@ -34,7 +35,8 @@ cudaError_t encode_tensor_map_2d(CUtensorMap* map, const float* base, int cols, 
     const cuuint32_t box[2] = { static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows) };
     const cuuint32_t elem[2] = { 1, 1 };
     const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, elem,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }

@@ -1,0 +1,81 @@
+"""The tcgen05 kind::tf32 path against a double-precision host product.
+
+Tolerance: TF32 keeps 10 mantissa bits and the tensor core takes the FP32 operands
+as they are (the low 13 bits are dropped, not rounded), so every product carries a
+relative error of up to 2^-9 with a bias of about -2^-10 that does not average out.
+The stated bound is 2e-3 relative Frobenius error against the FP64 product of the
+same FP32 inputs; measured values are around 7e-4.
+"""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+TF32_TOL = 2e-3
+
+
+def rel_err(got, want):
+    return float(np.linalg.norm(got.astype(np.float64) - want) / np.linalg.norm(want))
+
+
+def run(pkg, p, layout_ns=128, fmt=None):
+    op = pkg.NMSpMM.from_problem(p, layout_ns=layout_ns, fmt=fmt)
+    C = op.matmul(torch.from_numpy(p.A_km).cuda(), path=pkg.PATH_TF32)
+    torch.cuda.synchronize()
+    assert pkg.device_status() == 0
+    return C.cpu().numpy()
+
+
+@pytest.mark.parametrize("n_keep,fmt", [(16, 0), (32, 0), (8, 0), (8, 1), (4, 1)])
+@pytest.mark.parametrize("layout", [32, 64, 128])
+def test_tf32_every_supported_ratio_and_layout(pkg, orc, n_keep, fmt, layout):
+    p = pkg.formats.make_random(256, 512, 512, n_keep, seed=200 + n_keep)
+    want = orc.nm_gemm_f64(p.A_km, p.B_col, p.D_col)
+    err = rel_err(run(pkg, p, layout_ns=layout, fmt=fmt), want)
+    assert err <= TF32_TOL, err
+
+
+@pytest.mark.parametrize("M,N", [(200, 640), (16, 128), (128, 96), (392, 1056)])
+def test_tf32_ragged_rows_and_columns(pkg, orc, M, N):
+    p = pkg.formats.make_random(M, N, 256, 8, seed=210)
+    want = orc.nm_gemm_f64(p.A_km, p.B_col, p.D_col)
+    assert rel_err(run(pkg, p, layout_ns=32), want) <= TF32_TOL
+
+
+def test_tf32_single_window(pkg, orc):
+    p = pkg.formats.make_random(128, 256, 64, 8, seed=211)
+    assert rel_err(run(pkg, p), orc.nm_gemm_f64(p.A_km, p.B_col, p.D_col)) <= TF32_TOL
+
+
+def test_tf32_is_deterministic_and_close_to_the_exact_path(pkg):
+    p = pkg.formats.make_random(256, 512, 1024, 8, seed=212)
+    op = pkg.NMSpMM.from_problem(p)
+    A = torch.from_numpy(p.A_km).cuda()
+    a = op.matmul(A, path=pkg.PATH_TF32)
+    b = op.matmul(A, path=pkg.PATH_TF32)
+    exact = op.matmul(A)
+    assert torch.equal(a, b)
+    assert float((a - exact).norm() / exact.norm()) <= TF32_TOL
+
+
+def test_tf32_unsupported_ratio_is_refused(pkg):
+    p = pkg.formats.make_random(128, 256, 256, 12, seed=213)
+    op = pkg.NMSpMM.from_problem(p)
+    with pytest.raises(pkg.NMSpMMError) as e:
+        op.matmul(torch.from_numpy(p.A_km).cuda(), path=pkg.PATH_TF32)
+    assert e.value.status == pkg.UNSUPPORTED
+
+
+@pytest.mark.parametrize("n_keep", [16, 8, 4])
+def test_tf32_square_4096_full_size(pkg, orc, n_keep):
+    p = pkg.formats.make_random(4096, 4096, 4096, n_keep, seed=80)
+    op = pkg.NMSpMM.from_problem(p)
+    A = torch.from_numpy(p.A_km).cuda()
+    C = op.matmul(A, path=pkg.PATH_TF32)
+    rows = np.array([0, 1, 127, 128, 2047, 2048, 4095])
+    want = orc.nm_gemm_f64(np.ascontiguousarray(p.A_km[:, rows]), p.B_col, p.D_col)
+    assert rel_err(C[torch.from_numpy(rows).cuda()].cpu().numpy(), want) <= TF32_TOL
+    exact = op.matmul(A)
+    assert float((C - exact).norm() / exact.norm()) <= TF32_TOL
+    assert pkg.device_status() == 0

@@ -117,7 +117,7 @@ def test_split_k_fills_the_machine_for_skinny_shapes(pkg):
 
 @pytest.mark.parametrize("kw,status", [
     (dict(M=0), 1), (dict(N=100), 1), (dict(K=48), 1), (dict(M=6), 1), (dict(layout_ns=96), 1),
-    (dict(n_keep=10), 2), (dict(n_keep=16, fmt=1), 2), (dict(n_keep=4, fmt=0), 2), (dict(path=1), 2),
+    (dict(n_keep=10), 2), (dict(n_keep=16, fmt=1), 2), (dict(n_keep=4, fmt=0), 2), (dict(path=2), 2), (dict(path=1, n_keep=12), 2),
     (dict(N=192, layout_ns=128), 1), (dict(K=96, n_keep=8, fmt=1), 1), (dict(split_k=-1), 1),
 ])
 def test_bad_descriptions_are_rejected(pkg, kw, status):
