@@ -336,6 +336,32 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                               "dense_equivalent_tflops": 2.0 * M * n_local * K / (t * 1e-3) / 1e12,
                               "roofline_frac": max(tf, tm) / (t * 1e-3)})
 
+    # ---- the tensor-core path on the same workload (N=1 only) ------------------------
+    tf32 = None
+    if world == 1:
+        tf32_peak = float(peaks.get("bf16_tflops", 1590.0)) / 2.0      # dense TF32 = half the dense bf16 rate
+        rows = []
+        for n_keep in (16, 8, 4):
+            pr = p if n_keep == HEADLINE_KEEP else pkg.formats.make_random(M, n_local, K, n_keep, seed=0)
+            opr = op if n_keep == HEADLINE_KEEP else pkg.NMSpMM.from_problem(pr, layout_ns=128)
+            fn = lambda i, o=opr: o.matmul(A_sets[i % SETS], out=C_sets[i % SETS], path=pkg.PATH_TF32)
+            for i in range(3):
+                fn(i)
+            t = time_steps(torch, fn, 20) / 20
+            uf = 2.0 * M * n_local * pr.W
+            tf, tm = uf / (tf32_peak * 1e12), algorithmic_bytes(M, n_local, K, n_keep) / (hbm_gbs * 1e9)
+            exact = opr.matmul(A_sets[0])
+            err = float((opr.matmul(A_sets[0], path=pkg.PATH_TF32) - exact).norm() / exact.norm())
+            rows.append({"n_keep": n_keep, "path": "tf32", "ms": t, "useful_tflops": uf / (t * 1e-3) / 1e12,
+                         "dense_equivalent_tflops": 2.0 * M * n_local * K / (t * 1e-3) / 1e12,
+                         "roofline_frac": max(tf, tm) / (t * 1e-3), "rel_err_vs_fp32_path": err})
+        tf32 = {"kernel": "nm_gemm_tf32_kernel, tile 128x128, tcgen05.mma kind::tf32 M128 N32 K8, A gathered into TMEM",
+                "bound": "tensor", "peak": tf32_peak, "unit": "TFLOP/s",
+                "peak_source": "half of the measured dense bf16 rate in MEASURED_PEAKS.json (burst)"
+                               if "bf16_tflops" in peaks else "half of the fallback 1590 TFLOP/s bf16",
+                "tolerance": "2e-3 relative Frobenius error against the FP64 host product (tests/test_gpu_tf32.py)",
+                "per_ratio": rows}
+
     # ---- end to end through the host-buffer entry point ------------------------------
     hA = torch.from_numpy(p.A_km).pin_memory()
     hB = torch.from_numpy(p.BT).pin_memory()
@@ -371,7 +397,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                        "l2": f"operands rotate over {SETS} sets of A and C (3 x 128 MB > 126 MB L2); no flush"},
             "dense_equivalent_tflops": world * 2.0 * M * n_local * K / (ms_per_step * 1e-3) / 1e12,
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "e2e_rel_err_vs_resident": e2e_err,
-            "gpu_launches": args.steps, "clocks": sampler.summary(), "per_ratio": per_ratio,
+            "gpu_launches": args.steps, "clocks": sampler.summary(), "per_ratio": per_ratio, "tf32": tf32,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -129,13 +129,17 @@ static int make_plan(const nmspmm_gemm_desc* d, int sms, Plan* p)
     if (sms <= 0) sms = 148;
     if (d->path == NMSPMM_PATH_TF32) {
         // Tensor-core path: one 128 x 256 tile per CTA over all k windows (split_k is ignored).
+        // tile 128 x 128 (two CTAs per SM cover each other's hand-off latencies) unless
+        // the caller asks for the 128 x 256 tile
+        const int want_ns = (d->tile == kTile128x256) ? 256 : 128;
         for (int i = 0; i < kTf32VariantCount; ++i)
-            if (kTf32Variants[i].n_keep == d->n_keep && kTf32Variants[i].mode == mode) p->tv = &kTf32Variants[i];
+            if (kTf32Variants[i].n_keep == d->n_keep && kTf32Variants[i].mode == mode && kTf32Variants[i].ns == want_ns)
+                p->tv = &kTf32Variants[i];
         if (!p->tv) return NMSPMM_UNSUPPORTED;
         p->ws = p->tv->ws;
         p->W = d->K / 32 * d->n_keep;
         p->n_win = p->W / p->ws;
-        p->tiles_x = (d->N + 255) / 256;
+        p->tiles_x = (d->N + p->tv->ns - 1) / p->tv->ns;
         p->tiles_y = (d->M + 127) / 128;
         const long long nt = static_cast<long long>(p->tiles_x) * p->tiles_y;
         if (nt >= (1LL << 30)) return NMSPMM_UNSUPPORTED;
@@ -411,7 +415,7 @@ int nmspmm_gemm_plan(const nmspmm_gemm_desc* desc, nmspmm_gemm_plan_info* out)
     if (rc != NMSPMM_OK) return rc;
     out->tile = p.v ? p.v->tile_id : 0;
     out->tile_m = p.v ? p.v->ms : 128;
-    out->tile_n = p.v ? p.v->ns : 256;
+    out->tile_n = p.v ? p.v->ns : p.tv->ns;
     out->split_k = p.split_k > 0 ? p.split_k
                                  : (p.n_tiles > p.n_dp ? (p.n_virtual - p.n_dp + p.n_tiles - p.n_dp - 1) / (p.n_tiles - p.n_dp) : 1);
     out->n_dp = p.n_dp;

@@ -100,6 +100,41 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     return true;
 }
 
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Same contract as mbar_wait_bounded, but polls without letting the hardware suspend the
+// thread: for hand-offs that are expected within a few hundred cycles, where the wake-up
+// latency of a suspended wait would dominate.
+__device__ __forceinline__ bool mbar_spin_bounded(uint32_t bar, uint32_t parity, uint32_t abort_word)
+{
+    if (mbar_test_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    unsigned spins = 0;
+    while (!mbar_test_wait(bar, parity)) {
+        if ((++spins & 1023u) == 0u) {
+            if (lds_volatile_s32(abort_word)) return false;
+            if (clock64() - t0 > kWaitCycleLimit) {
+                sts_volatile_s32(abort_word, 1);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
 // Untiled bulk copy global -> shared, completion counted in bytes on an mbarrier.
 // Both addresses 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src_gmem, uint32_t bytes, uint32_t bar)

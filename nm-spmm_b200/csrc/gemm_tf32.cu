@@ -8,10 +8,10 @@
 //               unswizzled), one swizzled tiled copy per vector of its WS x 32
 //               block of B (32-byte chunks swizzled within 128-byte rows: the one legal
 //               layout of an MN-major TF32 operand), bulk copies of the packed indices and column_info lists.
-//   warps 2-9   two sets of four gather warps.  Thread = row of the tile.  For one unit
-//               (vector, group of 8 compressed rows) a thread reads its row's 8 gathered
+//   warps 2-9   two sets of four gather warps that take the vectors in turn.  Thread = row
+//               of the tile.  For one vector and window a thread reads its row's WS gathered
 //               values from As (conflict-free: consecutive lanes, consecutive words) and
-//               stores them as 8 TMEM columns (tcgen05.st): the A operand of one MMA.
+//               stores them as WS TMEM columns (tcgen05.st): the A operand of WS/8 MMAs.
 //   warp 1      one thread issues tcgen05.mma kind::tf32, M128 N32 K8, A from TMEM, B from
 //               shared memory, D = the vector's 32 accumulator columns in TMEM, and commits
 //               to mbarriers that hand the A buffers and the stage back.
@@ -26,36 +26,39 @@
 
 namespace nmspmm {
 
-template <int WS, int KS_, int MODE>
+template <int WS, int KS_, int MODE, int QT_>
 struct Tf32Cfg {
-    static constexpr int MS = 128, NS = 256, QT = NS / 32;
+    static constexpr int MS = 128, QT = QT_, NS = QT * 32;   // QT = 8: one CTA per SM; QT = 4: two
     static constexpr int KS = KS_;
     static constexpr int G = WS / 8;                       // MMAs (K = 8 each) per vector and window
     static_assert(WS % 8 == 0, "kind::tf32 contracts 8 rows per instruction");
     static constexpr int B_BYTES = QT * WS * 128;          // per vector WS rows of 128 bytes, swizzled; multiple of 1024
     static constexpr int A_BYTES = KS * MS * 4;
-    static constexpr int D_BYTES = ((WS * 8 * 4 + 127) / 128) * 128;
+    static constexpr int D_BYTES = ((WS * (QT > 4 ? QT : 4) * 4 + 127) / 128) * 128;
     static constexpr int CI_BYTES = (MODE == kModeHigh) ? QT * 256 : 0;
     static constexpr int STAGE_BYTES = ((B_BYTES + A_BYTES + D_BYTES + CI_BYTES + 1023) / 1024) * 1024;
-    static constexpr int ST0 = (196 * 1024) / STAGE_BYTES;
+    static constexpr int CTAS_PER_SM = (QT == 8) ? 1 : 2;
+    static constexpr int ST0 = ((CTAS_PER_SM == 1 ? 196 : 100) * 1024) / STAGE_BYTES;
     static constexpr int STAGES = ST0 > 4 ? 4 : (ST0 < 2 ? 2 : ST0);
-    static constexpr int NB = 4;                           // A buffers (8 TMEM columns each) per gather set
+    static constexpr int TMEM_COLS = 512 / CTAS_PER_SM;    // each resident CTA allocates its share
+    static constexpr int NB0 = (TMEM_COLS - NS) / (2 * WS);
+    static constexpr int NB = NB0 > 4 ? 4 : NB0;           // A buffers (WS TMEM columns each) per gather set
     static constexpr int GATHER_WARPS = 8;
     static constexpr int THREADS = (2 + GATHER_WARPS) * 32;
     static constexpr int TAB_BYTES = GATHER_WARPS * QT * WS * 4;   // per-warp table of gather offsets
     static constexpr int NBARS = 2 * STAGES + 4 * NB + 1;
     static constexpr int CTRL_BYTES = ((NBARS * 8 + 16 + 127) / 128) * 128;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + TAB_BYTES + CTRL_BYTES + 1024;   // + alignment slack
-    static constexpr int TMEM_COLS = 512;
     static constexpr int ACOL0 = NS;                       // first A-buffer column
+    static_assert(NB >= 1 && NS + 2 * NB * WS <= TMEM_COLS, "A buffers do not fit beside the accumulators");
     static constexpr bool HALF = false;
 };
 
-template <int WS, int KS_, int MODE>
-__global__ void __launch_bounds__((Tf32Cfg<WS, KS_, MODE>::THREADS), 1)
+template <int WS, int KS_, int MODE, int QT_>
+__global__ void __launch_bounds__((Tf32Cfg<WS, KS_, MODE, QT_>::THREADS), (Tf32Cfg<WS, KS_, MODE, QT_>::CTAS_PER_SM))
 nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b)
 {
-    using Cfg = Tf32Cfg<WS, KS_, MODE>;
+    using Cfg = Tf32Cfg<WS, KS_, MODE, QT_>;
     constexpr int MS = Cfg::MS, NS = Cfg::NS, QT = Cfg::QT, KS = Cfg::KS, G = Cfg::G, STAGES = Cfg::STAGES, NB = Cfg::NB;
 
     extern __shared__ unsigned char smem_raw[];
@@ -140,23 +143,23 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
             const uint32_t st = ring + s * Cfg::STAGE_BYTES;
             int set = 0;
             for (int v = 0; v < live_vecs && alive; ++v) {
+                // one chunk = the whole window of one vector: G MMAs on one A buffer
+                const unsigned c = set ? cnt1 : cnt0;
+                const int buf = set * NB + static_cast<int>(c % NB);
+                ok = mbar_spin_bounded(bar_aready + buf * 8, (c / NB) & 1, abort_word);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) { alive = false; break; }
+                tc_fence_after_sync();
+                if (lane == 0) {
 #pragma unroll
-                for (int gi = 0; gi < G; ++gi) {
-                    const unsigned c = set ? cnt1 : cnt0;
-                    const int buf = set * NB + static_cast<int>(c % NB);
-                    ok = mbar_wait_bounded(bar_aready + buf * 8, (c / NB) & 1, abort_word);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) { alive = false; break; }
-                    tc_fence_after_sync();
-                    if (lane == 0) {
-                        umma_tf32_ts(tmem_addr(tmem, 0, v * 32), tmem_addr(tmem, 0, Cfg::ACOL0 + buf * 8),
+                    for (int gi = 0; gi < G; ++gi)
+                        umma_tf32_ts(tmem_addr(tmem, 0, v * 32), tmem_addr(tmem, 0, Cfg::ACOL0 + buf * WS + gi * 8),
                                      umma_desc_mn_tf32(st + v * (WS * 128) + gi * 1024), idesc, (it | gi) != 0);
-                        tc_commit(bar_afree + buf * 8);    // the A buffer is free once this MMA has read it
-                    }
-                    __syncwarp();
-                    if (set) ++cnt1; else ++cnt0;
-                    set ^= 1;
+                    tc_commit(bar_afree + buf * 8);        // the A buffer is free once these MMAs have read it
                 }
+                __syncwarp();
+                if (set) ++cnt1; else ++cnt0;
+                set ^= 1;
             }
             if (lane == 0) tc_commit(bar_empty + s * 8);   // the window's B blocks have been read
             __syncwarp();
@@ -190,34 +193,30 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
                 sts_volatile_s32(tab + e * 4, k * (MS * 4));
             }
             __syncwarp();
-            int unit_set = 0;
-            for (int v = 0; v < live_vecs && alive; ++v) {
+            for (int v = set; v < live_vecs && alive; v += 2) {     // the two sets take the vectors in turn
+                const int buf = set * NB + static_cast<int>(cnt % NB);
+                if (cnt >= NB) {
+                    ok = mbar_spin_bounded(bar_afree + buf * 8, ((cnt / NB) - 1) & 1, abort_word);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) { alive = false; break; }
+                    tc_fence_after_sync();
+                }
+                const uint32_t base = as + row * 4;
 #pragma unroll
                 for (int gi = 0; gi < G; ++gi) {
-                    if (unit_set == set) {
-                        const int buf = set * NB + static_cast<int>(cnt % NB);
-                        if (cnt >= NB) {
-                            ok = mbar_wait_bounded(bar_afree + buf * 8, ((cnt / NB) - 1) & 1, abort_word);
-                            ok = __all_sync(0xffffffffu, ok);
-                            if (!ok) { alive = false; break; }
-                            tc_fence_after_sync();
-                        }
-                        const int4 o0 = lds_i4(tab + (v * WS + gi * 8) * 4), o1 = lds_i4(tab + (v * WS + gi * 8 + 4) * 4);
-                        const uint32_t base = as + row * 4;
-                        uint32_t a[8];
-                        a[0] = lds_u32(base + o0.x); a[1] = lds_u32(base + o0.y);
-                        a[2] = lds_u32(base + o0.z); a[3] = lds_u32(base + o0.w);
-                        a[4] = lds_u32(base + o1.x); a[5] = lds_u32(base + o1.y);
-                        a[6] = lds_u32(base + o1.z); a[7] = lds_u32(base + o1.w);
-                        tmem_st_x8(tmem_addr(tmem, quad * 32, Cfg::ACOL0 + buf * 8), a);
-                        tmem_wait_st();
-                        tc_fence_before_sync();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(bar_aready + buf * 8);
-                        ++cnt;
-                    }
-                    unit_set ^= 1;
+                    const int4 o0 = lds_i4(tab + (v * WS + gi * 8) * 4), o1 = lds_i4(tab + (v * WS + gi * 8 + 4) * 4);
+                    uint32_t a[8];
+                    a[0] = lds_u32(base + o0.x); a[1] = lds_u32(base + o0.y);
+                    a[2] = lds_u32(base + o0.z); a[3] = lds_u32(base + o0.w);
+                    a[4] = lds_u32(base + o1.x); a[5] = lds_u32(base + o1.y);
+                    a[6] = lds_u32(base + o1.z); a[7] = lds_u32(base + o1.w);
+                    tmem_st_x8(tmem_addr(tmem, quad * 32, Cfg::ACOL0 + buf * WS + gi * 8), a);
                 }
+                tmem_wait_st();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_aready + buf * 8);
+                ++cnt;
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty + s * 8);     // this warp has finished reading As of the stage
@@ -228,10 +227,10 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
         if (ok) {
             tc_fence_after_sync();
             const int r = bi + row;
-            const int half = gw >> 2;                      // columns [0,128) or [128,256)
+            const int half = gw >> 2;                      // lower or upper half of the tile's columns
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                const int col = half * 128 + c * 32;
+            for (int c = 0; c < QT / 2; ++c) {
+                const int col = half * (NS / 2) + c * 32;
                 if (col >= live_vecs * 32) break;
                 uint32_t v[32];
                 tmem_ld_x32(tmem_addr(tmem, quad * 32, col), v);
@@ -256,11 +255,11 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
     }
 }
 
-template <int NKEEP, int WS, int KS, int MODE>
+template <int WS, int KS, int MODE, int QT>
 static cudaError_t launch_tf32(const GemmArgs& a, int tiles, cudaStream_t st)
 {
-    using Cfg = Tf32Cfg<WS, KS, MODE>;
-    auto kernel = nm_gemm_tf32_kernel<WS, KS, MODE>;
+    using Cfg = Tf32Cfg<WS, KS, MODE, QT>;
+    auto kernel = nm_gemm_tf32_kernel<WS, KS, MODE, QT>;
     static bool configured[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -279,12 +278,16 @@ static cudaError_t launch_tf32(const GemmArgs& a, int tiles, cudaStream_t st)
     return cudaGetLastError();
 }
 
+#define NMSPMM_TF32_VARIANT(NKEEP, WS, KS, MODE, QT)                                                        \
+    { NKEEP, WS, KS, MODE, QT * 32, Tf32Cfg<WS, KS, MODE, QT>::SMEM_BYTES, Tf32Cfg<WS, KS, MODE, QT>::STAGES, \
+      &launch_tf32<WS, KS, MODE, QT> }
+
 extern const Tf32Variant kTf32Variants[] = {
-    { 32, 32, 32, kModeLow, Tf32Cfg<32, 32, kModeLow>::SMEM_BYTES, Tf32Cfg<32, 32, kModeLow>::STAGES, &launch_tf32<32, 32, 32, kModeLow> },
-    { 16, 16, 32, kModeLow, Tf32Cfg<16, 32, kModeLow>::SMEM_BYTES, Tf32Cfg<16, 32, kModeLow>::STAGES, &launch_tf32<16, 16, 32, kModeLow> },
-    { 8, 8, 32, kModeLow, Tf32Cfg<8, 32, kModeLow>::SMEM_BYTES, Tf32Cfg<8, 32, kModeLow>::STAGES, &launch_tf32<8, 8, 32, kModeLow> },
-    { 8, 16, 64, kModeHigh, Tf32Cfg<16, 64, kModeHigh>::SMEM_BYTES, Tf32Cfg<16, 64, kModeHigh>::STAGES, &launch_tf32<8, 16, 64, kModeHigh> },
-    { 4, 8, 64, kModeHigh, Tf32Cfg<8, 64, kModeHigh>::SMEM_BYTES, Tf32Cfg<8, 64, kModeHigh>::STAGES, &launch_tf32<4, 8, 64, kModeHigh> },
+    NMSPMM_TF32_VARIANT(32, 32, 32, kModeLow, 8),  NMSPMM_TF32_VARIANT(32, 32, 32, kModeLow, 4),
+    NMSPMM_TF32_VARIANT(16, 16, 32, kModeLow, 8),  NMSPMM_TF32_VARIANT(16, 16, 32, kModeLow, 4),
+    NMSPMM_TF32_VARIANT(8, 8, 32, kModeLow, 8),    NMSPMM_TF32_VARIANT(8, 8, 32, kModeLow, 4),
+    NMSPMM_TF32_VARIANT(8, 16, 64, kModeHigh, 8),  NMSPMM_TF32_VARIANT(8, 16, 64, kModeHigh, 4),
+    NMSPMM_TF32_VARIANT(4, 8, 64, kModeHigh, 8),   NMSPMM_TF32_VARIANT(4, 8, 64, kModeHigh, 4),
 };
 extern const int kTf32VariantCount = sizeof(kTf32Variants) / sizeof(kTf32Variants[0]);
 

@@ -32,11 +32,12 @@ const FfmaVariant* find_ffma_variant(int tile_id, int n_keep, int mode);
 cudaError_t encode_tensor_map_2d(CUtensorMap* map, const float* base, int cols, int rows, int box_cols, int box_rows,
                                  int swizzle128 = 0);
 
-// One compiled TF32 tensor-core kernel variant (tile 128 x 256).
+// One compiled TF32 tensor-core kernel variant (tile 128 x ns).
 struct Tf32Variant {
     int n_keep;         // kept rows per 32-k window
     int ws, ks;         // rows of B / of A per staged window
     int mode;
+    int ns;             // tile columns: 256 (one CTA per SM) or 128 (two)
     int smem_bytes, stages;
     cudaError_t (*launch)(const GemmArgs&, int tiles, cudaStream_t st);
 };
