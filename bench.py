@@ -140,10 +140,15 @@ def physical_gpu_index(local_rank: int) -> int:
 # ------------------------------------------------------------------------------------
 
 def cpu_reference_impl():
+    """The reference's host multiply with every core this process may use (torchrun pins
+    OMP_NUM_THREADS to 1, which is not what a CPU baseline wants)."""
     import oracle
-    if oracle.have_reference():
-        return oracle.reference(), "reference"
-    return oracle.restatement(), "port"
+    impl, kind = (oracle.reference(), "reference") if oracle.have_reference() else (oracle.restatement(), "port")
+    try:
+        impl.set_num_threads(len(os.sched_getaffinity(0)))
+    except Exception:
+        pass
+    return impl, kind
 
 
 def cpu_sample(pkg, impl, p, rows: int):
@@ -404,6 +409,88 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         dist.destroy_process_group()
 
 
+WORKLOADS = {
+    # name: (M, N, K, n_keep, vec_len) -- the named configurations beside the square one
+    "llm16": (16, 11008, 4096, 8, 32), "llm64": (64, 11008, 4096, 8, 32), "llm256": (256, 11008, 4096, 8, 32),
+    "deepk": (128, 1024, 131072, 4, 32), "large": (8192, 28672, 8192, 8, 64),
+}
+
+
+def run_workload(args):
+    """One of the other named configurations on one GPU: per-launch device time with the L2
+    flushed between launches (these shapes are small enough to live in L2 otherwise), the
+    index packing timed alone, and the roofline fraction of each path."""
+    import torch
+
+    from __graft_entry__ import load_package
+    pkg = load_package(native=True)
+    torch.cuda.set_device(0)
+    M, N, K, n_keep, vec = WORKLOADS[args.workload]
+    p = pkg.formats.make_random(M, N, K, n_keep, seed=0, vec_len=vec, a_dist="normal" if args.workload.startswith("llm") else "uniform")
+    raw = torch.from_numpy(p.DT).cuda()
+    useful, abytes = p.useful_flops(), algorithmic_bytes(M, N, K, n_keep)
+    # Replicas of the sparse operand and of C, cycled launch after launch, so that a launch
+    # never finds its operands in the 126 MB L2; the launches are captured in a CUDA graph so
+    # that the device time is not padded by host launch latency (some of these kernels take
+    # tens of microseconds).
+    n_rep = max(2, min(8, -(-(300 << 20) // abytes)))
+    reps = n_rep * max(2, args.steps // n_rep)
+
+    def graph_time(fns):
+        for f in fns:
+            f()
+        torch.cuda.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            for i in range(reps):
+                fns[i % len(fns)]()
+        gr.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        gr.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    raws = [raw.clone() for _ in range(n_rep)]
+    if pkg.format_of(n_keep) == pkg.FORMAT_HIGH:
+        outs = [pkg.preprocess_high_device(r, 32, n_keep, 128, fuse_trans_index=True) for r in raws]
+        packs = [lambda r=r, o=o: pkg.preprocess_high_device(r, 32, n_keep, 128, fuse_trans_index=True, out=o[0], column_info=o[1])
+                 for r, o in zip(raws, outs)]
+    else:
+        outs = [pkg.preprocess_low_device(r, 128) for r in raws]
+        packs = [lambda r=r, o=o: pkg.preprocess_low_device(r, 128, out=o) for r, o in zip(raws, outs)]
+    pack_ms = graph_time(packs)
+    ops = [pkg.NMSpMM.from_problem(p, layout_ns=128) for _ in range(n_rep)]
+    A = torch.from_numpy(p.A_km).cuda()
+    Cs = [torch.empty((M, N), dtype=torch.float32, device="cuda") for _ in range(n_rep)]
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    hbm = float(peaks.get("hbm_gbs", 6650.0)) * 1e9
+    fp32_peak = max(pkg.measure_ffma_peak(False), pkg.measure_ffma_peak(True)) * 1e12
+    tf32_peak = float(peaks.get("bf16_tflops", 1590.0)) / 2.0 * 1e12
+    pack_bytes = 2 * raw.numel() * 4 + (outs[0][1].numel() * 4 if isinstance(outs[0], tuple) else 0)
+    out = {"workload": args.workload, "M": M, "N": N, "K": K, "n_keep": n_keep, "vec_len": vec,
+           "index_packing_ms": pack_ms, "index_packing_gbs": pack_bytes / (pack_ms * 1e-3) / 1e9,
+           "algorithmic_bytes": abytes, "useful_flops": useful, "hbm_time_us": abytes / hbm * 1e6,
+           "l2": f"{n_rep} replicas of B, indices and C cycled (working set {n_rep * abytes >> 20} MB); "
+                 f"{reps} launches replayed from a CUDA graph"}
+    for name, path, peak in (("fp32", pkg.PATH_FP32, fp32_peak), ("tf32", pkg.PATH_TF32, tf32_peak)):
+        fns = [lambda o=o, c=c: o.matmul(A, out=c, path=path, tile=args.tile, split_k=args.split_k) for o, c in zip(ops, Cs)]
+        ms = graph_time(fns)
+        plan = pkg.plan(ops[0].desc(M, path=path, tile=args.tile, split_k=args.split_k))
+        out[name] = {"ms": ms, "useful_tflops": useful / (ms * 1e-3) / 1e12, "bytes_per_s_gbs": abytes / (ms * 1e-3) / 1e9,
+                     "roofline_frac": max(useful / peak, abytes / hbm) / (ms * 1e-3),
+                     "bound": "hbm" if abytes / hbm > useful / peak else "flops",
+                     "tile": [plan.tile_m, plan.tile_n], "ctas": plan.grid, "whole_tiles": plan.n_dp}
+    assert pkg.device_status() == 0
+    print(json.dumps(out), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -413,6 +500,8 @@ def main():
     ap.add_argument("--kernel-only", action="store_true",
                     help="only the resident-operand steps (profiling runs): no e2e, CPU baseline or ratio sweep")
     ap.add_argument("--n-keep", type=int, default=HEADLINE_KEEP, help="kept rows per 32-window for --kernel-only runs")
+    ap.add_argument("--workload", default="", choices=[""] + sorted(WORKLOADS),
+                    help="measure one of the other named configurations on one GPU instead of the square one")
     ap.add_argument("--path", default="fp32", choices=["fp32", "tf32"], help="arithmetic of --kernel-only runs")
     ap.add_argument("--tile", type=int, default=0, help="force a CTA tile id (tuning runs)")
     ap.add_argument("--split-k", type=int, default=0, help="force the number of K slices (tuning runs)")
@@ -420,7 +509,9 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference":
+    if args.workload:
+        run_workload(args)
+    elif args.impl == "reference":
         run_reference_arm(args, rank, world)
     else:
         run_ours(args, rank, world, local_rank)
