@@ -152,3 +152,50 @@ def test_square_4096_full_size(pkg, orc, n_keep):
     lin = (C12 - (C + C2)).norm() / C12.norm()
     assert float(lin) <= 2e-6
     assert pkg.device_status() == 0
+
+
+def test_llm_linear_full_size(pkg, orc):
+    """LLM-linear configuration at full size (K = 4096, N = 11008, 8:32 by per-vector L2
+    magnitude): tokens 16 and 256 against the checker, both paths of the split schedule."""
+    base = pkg.formats.make_llm_linear(256, seed=81)
+    op = pkg.NMSpMM.from_problem(base)
+    for tokens in (16, 256):
+        A_km = np.ascontiguousarray(base.A_km[:, :tokens])
+        want = orc.nm_gemm_f32(A_km, base.B_col, base.D_col)
+        got = op.matmul(torch.from_numpy(A_km).cuda()).cpu().numpy()
+        assert rel_err(got, want) <= FP32_TOL, tokens
+        again = op.matmul(torch.from_numpy(A_km).cuda()).cpu().numpy()
+        assert np.array_equal(got, again)
+    assert pkg.device_status() == 0
+
+
+def test_deep_k_full_size(pkg, orc):
+    """Deep-K configuration at full size: A 128 x 131072, B 131072 x 1024, 4:32."""
+    p = pkg.formats.make_random(128, 1024, 131072, 4, seed=82)
+    want = orc.nm_gemm_f32(p.A_km, p.B_col, p.D_col)
+    op = pkg.NMSpMM.from_problem(p)
+    A = torch.from_numpy(p.A_km).cuda()
+    got = op.matmul(A).cpu().numpy()
+    assert rel_err(got, want) <= FP32_TOL
+    for split in (7, 32):                       # explicit K slices agree with the automatic schedule
+        assert rel_err(op.matmul(A, split_k=split).cpu().numpy(), want) <= FP32_TOL
+    assert pkg.device_status() == 0
+
+
+def test_large_sharded_full_size(pkg, orc):
+    """Large configuration at full size (8192 x 28672 x 8192, 8:32, V = 64): sampled rows
+    against the checker, and the column slabs of a 4-way shard (computed one after the other
+    on this GPU through the package's partition code) equal the unsharded result bit for bit."""
+    M, N, K = 8192, 28672, 8192
+    p = pkg.formats.make_random(M, N, K, 8, seed=83, vec_len=64)
+    A = torch.from_numpy(p.A_km).cuda()
+    full = pkg.NMSpMM.from_problem(p).matmul(A)
+    rows = np.array([0, 127, 128, 4095, 4096, 8191])
+    want = orc.nm_gemm_f32(np.ascontiguousarray(p.A_km[:, rows]), p.B_col, p.D_col)
+    assert rel_err(full[torch.from_numpy(rows).cuda()].cpu().numpy(), want) <= FP32_TOL
+    world = 4
+    for rank in (0, 3):
+        bt, dt, (c0, c1) = pkg.sharding.shard_operands(p.BT, p.DT, rank, world, 128)
+        slab = pkg.NMSpMM(bt, dt, K, 8, 128).matmul(A)
+        assert torch.equal(slab, full[:, c0:c1]), rank
+    assert pkg.device_status() == 0
