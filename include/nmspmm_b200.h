@@ -175,8 +175,12 @@ int nmspmm_gemm_plan(const nmspmm_gemm_desc* desc, nmspmm_gemm_plan_info* out);
 /* End-to-end form on HOST buffers: copies A, B, the raw DT [W][Q] and nothing else
  * to the device, packs the indices there, multiplies and copies C back.  Device
  * buffers are kept in a per-thread arena that grows on demand (this function
- * allocates).  Work is issued on `stream` (NULL = a private stream of the arena) and
- * the function returns after that stream has drained.  This is what a caller of the
+ * allocates).  Work is ordered after what `stream` holds at the call (NULL = a private
+ * stream of the arena) and the function returns after all of it has drained.  From
+ * M = 2048 up, A goes in and C comes out in row blocks on two copy streams of the arena
+ * while other blocks are multiplied, so the transfers of both directions overlap the
+ * arithmetic; the pageable-or-pinned state of the host buffers decides whether the
+ * copies are truly asynchronous.  This is what a caller of the
  * reference's test driver does around its launcher (tests/test_nmspmm.cu:72-101). */
 int nmspmm_gemm_host(const nmspmm_gemm_desc* desc,
                      const float* A_host, const float* B_host, const int* DT_host, float* C_host,

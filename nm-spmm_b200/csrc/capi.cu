@@ -244,11 +244,14 @@ static int scratch_reserve(size_t bytes, void** out)
 }
 
 // ---- arena of nmspmm_gemm_host ---------------------------------------------------
+constexpr int kHostChunks = 8;       // at most this many row blocks of A / C are pipelined by nmspmm_gemm_host
 struct Arena {
     void* ptr = nullptr;
     size_t bytes = 0;
     int device = -1;
-    cudaStream_t stream = nullptr;
+    cudaStream_t stream = nullptr;          // compute (when the caller passes none)
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr, in_done[kHostChunks] = {}, mm_done[kHostChunks] = {};
 };
 static thread_local Arena tl_arena;
 
@@ -269,8 +272,15 @@ static int arena_reserve(size_t bytes, unsigned char** out, cudaStream_t* st)
         if (e != cudaSuccess) return cuda_fail(e);
         a.bytes = bytes;
         if (a.device != dev || !a.stream) {
-            e = cudaStreamCreateWithFlags(&a.stream, cudaStreamNonBlocking);
-            if (e != cudaSuccess) return cuda_fail(e);
+            if ((e = cudaStreamCreateWithFlags(&a.stream, cudaStreamNonBlocking)) != cudaSuccess) return cuda_fail(e);
+            if ((e = cudaStreamCreateWithFlags(&a.copy_in, cudaStreamNonBlocking)) != cudaSuccess) return cuda_fail(e);
+            if ((e = cudaStreamCreateWithFlags(&a.copy_out, cudaStreamNonBlocking)) != cudaSuccess) return cuda_fail(e);
+            if ((e = cudaEventCreateWithFlags(&a.fork, cudaEventDisableTiming)) != cudaSuccess) return cuda_fail(e);
+            if ((e = cudaEventCreateWithFlags(&a.join, cudaEventDisableTiming)) != cudaSuccess) return cuda_fail(e);
+            for (int i = 0; i < kHostChunks; ++i) {
+                if ((e = cudaEventCreateWithFlags(&a.in_done[i], cudaEventDisableTiming)) != cudaSuccess) return cuda_fail(e);
+                if ((e = cudaEventCreateWithFlags(&a.mm_done[i], cudaEventDisableTiming)) != cudaSuccess) return cuda_fail(e);
+            }
         }
         a.device = dev;
     }
@@ -561,16 +571,37 @@ int nmspmm_gemm_host(const nmspmm_gemm_desc* desc, const float* A_host, const fl
     const int M = desc->M, N = desc->N, K = desc->K, W = p.W, Q = N / kVecLenHost;
     const bool high = desc->format == NMSPMM_FORMAT_HIGH;
     const int pn_m = 2 * desc->n_keep, pm_m = 64;
+
+    // Row blocks of A and C are pipelined: while block c is multiplied, block c+1 of A is on
+    // its way in and block c-1 of C on its way out (the link is full duplex).  A is col-major,
+    // so a row block is a strided 2-D copy that lands compact, [K][rows], on the device.
+    int n_chunks = M / 1024;
+    if (n_chunks > kHostChunks) n_chunks = kHostChunks;
+    if (n_chunks < 1) n_chunks = 1;
+    const int chunk_rows = (M / n_chunks + 127) / 128 * 128;
+    n_chunks = (M + chunk_rows - 1) / chunk_rows;
+    size_t ws_need = 0, counters_need = 0;
+    for (int c = 0; c < n_chunks; ++c) {
+        nmspmm_gemm_desc dc = *desc;
+        dc.M = (c + 1 < n_chunks) ? chunk_rows : M - c * chunk_rows;
+        Plan pc;
+        rc = make_plan(&dc, di->sms, &pc);
+        if (rc != NMSPMM_OK) return rc;
+        if (pc.counters_bytes + pc.partial_bytes > ws_need) ws_need = pc.counters_bytes + pc.partial_bytes;
+        if (pc.counters_bytes > counters_need) counters_need = pc.counters_bytes;
+    }
+
     const size_t a_b = round256(sizeof(float) * M * static_cast<size_t>(K));
     const size_t b_b = round256(sizeof(float) * W * static_cast<size_t>(N));
     const size_t d_b = round256(sizeof(int) * W * static_cast<size_t>(Q));
     const size_t c_b = round256(sizeof(float) * M * static_cast<size_t>(N));
     const size_t ci_b = high ? round256(sizeof(int) * (static_cast<size_t>(W / pn_m) * (N / desc->layout_ns) + 1) * pm_m) : 0;
-    const size_t ws_b = round256(p.counters_bytes + p.partial_bytes);
+    const size_t ws_b = round256(ws_need);
     unsigned char* base = nullptr;
     cudaStream_t st = nullptr;
     rc = arena_reserve(a_b + b_b + 2 * d_b + c_b + ci_b + ws_b, &base, &st);
     if (rc != NMSPMM_OK) return rc;
+    Arena& ar = tl_arena;
     if (stream) st = static_cast<cudaStream_t>(stream);
     float* dA = reinterpret_cast<float*>(base);
     float* dB = reinterpret_cast<float*>(base + a_b);
@@ -580,23 +611,44 @@ int nmspmm_gemm_host(const nmspmm_gemm_desc* desc, const float* A_host, const fl
     int* dCI = reinterpret_cast<int*>(base + a_b + b_b + 2 * d_b + c_b);
     unsigned char* dWS = base + a_b + b_b + 2 * d_b + c_b + ci_b;
     cudaError_t e;
-    if ((e = cudaMemcpyAsync(dDT, DT_host, sizeof(int) * W * static_cast<size_t>(Q), cudaMemcpyHostToDevice, st)) != cudaSuccess)
-        return cuda_fail(e);
-    if ((e = cudaMemcpyAsync(dB, B_host, sizeof(float) * W * static_cast<size_t>(N), cudaMemcpyHostToDevice, st)) != cudaSuccess)
-        return cuda_fail(e);
-    if ((e = cudaMemcpyAsync(dA, A_host, sizeof(float) * M * static_cast<size_t>(K), cudaMemcpyHostToDevice, st)) != cudaSuccess)
-        return cuda_fail(e);
+#define NMSPMM_TRY(call) do { if ((e = (call)) != cudaSuccess) return cuda_fail(e); } while (0)
+    // the copy streams start where the caller's stream is now
+    NMSPMM_TRY(cudaEventRecord(ar.fork, st));
+    NMSPMM_TRY(cudaStreamWaitEvent(ar.copy_in, ar.fork, 0));
+    NMSPMM_TRY(cudaStreamWaitEvent(ar.copy_out, ar.fork, 0));
+    // sparse operand first (it is needed by every block), then the blocks of A
+    NMSPMM_TRY(cudaMemcpyAsync(dDT, DT_host, sizeof(int) * W * static_cast<size_t>(Q), cudaMemcpyHostToDevice, st));
+    NMSPMM_TRY(cudaMemcpyAsync(dB, B_host, sizeof(float) * W * static_cast<size_t>(N), cudaMemcpyHostToDevice, st));
+    for (int c = 0; c < n_chunks; ++c) {
+        const int r0 = c * chunk_rows, rows = (c + 1 < n_chunks) ? chunk_rows : M - r0;
+        float* dst = dA + static_cast<size_t>(r0) * K;            // blocks are stored one after the other
+        NMSPMM_TRY(cudaMemcpy2DAsync(dst, sizeof(float) * rows, A_host + r0, sizeof(float) * M, sizeof(float) * rows, K,
+                                     cudaMemcpyHostToDevice, ar.copy_in));
+        NMSPMM_TRY(cudaEventRecord(ar.in_done[c], ar.copy_in));
+    }
     if (high)
         rc = nmspmm_preprocess_high_device(dDT, dD, dCI, 32, desc->n_keep, W, Q, desc->layout_ns, 1, pm_m, st);
     else
         rc = nmspmm_preprocess_low_device(dDT, dD, W, Q, desc->layout_ns, st);
     if (rc != NMSPMM_OK) return rc;
-    if (ws_b > 0 && (e = cudaMemsetAsync(dWS, 0, p.counters_bytes, st)) != cudaSuccess) return cuda_fail(e);
-    rc = nmspmm_gemm(desc, dA, dB, dD, high ? dCI : nullptr, dC, ws_b ? dWS : nullptr, ws_b, st);
-    if (rc != NMSPMM_OK) return rc;
-    if ((e = cudaMemcpyAsync(C_host, dC, sizeof(float) * M * static_cast<size_t>(N), cudaMemcpyDeviceToHost, st)) != cudaSuccess)
-        return cuda_fail(e);
-    if ((e = cudaStreamSynchronize(st)) != cudaSuccess) return cuda_fail(e);
+    if (counters_need > 0) NMSPMM_TRY(cudaMemsetAsync(dWS, 0, counters_need, st));   // the counters at the head of the scratch
+    for (int c = 0; c < n_chunks; ++c) {
+        const int r0 = c * chunk_rows, rows = (c + 1 < n_chunks) ? chunk_rows : M - r0;
+        nmspmm_gemm_desc dc = *desc;
+        dc.M = rows;
+        NMSPMM_TRY(cudaStreamWaitEvent(st, ar.in_done[c], 0));
+        rc = nmspmm_gemm(&dc, dA + static_cast<size_t>(r0) * K, dB, dD, high ? dCI : nullptr,
+                         dC + static_cast<size_t>(r0) * N, ws_b ? dWS : nullptr, ws_b, st);
+        if (rc != NMSPMM_OK) return rc;
+        NMSPMM_TRY(cudaEventRecord(ar.mm_done[c], st));
+        NMSPMM_TRY(cudaStreamWaitEvent(ar.copy_out, ar.mm_done[c], 0));
+        NMSPMM_TRY(cudaMemcpyAsync(C_host + static_cast<size_t>(r0) * N, dC + static_cast<size_t>(r0) * N,
+                                   sizeof(float) * rows * static_cast<size_t>(N), cudaMemcpyDeviceToHost, ar.copy_out));
+    }
+    NMSPMM_TRY(cudaEventRecord(ar.join, ar.copy_out));
+    NMSPMM_TRY(cudaStreamWaitEvent(st, ar.join, 0));
+    NMSPMM_TRY(cudaStreamSynchronize(st));
+#undef NMSPMM_TRY
     return nmspmm_device_status(nullptr, 1);
 }
 
@@ -618,7 +670,17 @@ int nmspmm_release_cached(void)
     if (tl_scratch.ptr) cudaFree(tl_scratch.ptr);
     tl_scratch = Scratch();
     if (tl_arena.ptr) cudaFree(tl_arena.ptr);
-    if (tl_arena.stream) cudaStreamDestroy(tl_arena.stream);
+    if (tl_arena.stream) {
+        cudaStreamDestroy(tl_arena.stream);
+        cudaStreamDestroy(tl_arena.copy_in);
+        cudaStreamDestroy(tl_arena.copy_out);
+        cudaEventDestroy(tl_arena.fork);
+        cudaEventDestroy(tl_arena.join);
+        for (int i = 0; i < kHostChunks; ++i) {
+            cudaEventDestroy(tl_arena.in_done[i]);
+            cudaEventDestroy(tl_arena.mm_done[i]);
+        }
+    }
     tl_arena = Arena();
     return NMSPMM_OK;
 }

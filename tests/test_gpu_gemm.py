@@ -120,6 +120,23 @@ def test_host_buffer_entry_point(pkg, orc):
         assert rel_err(C, orc.nm_gemm_f32(p.A_km, p.B_col, p.D_col)) <= FP32_TOL
 
 
+@pytest.mark.parametrize("M,n_keep", [(2308, 8), (3072, 16), (1024, 4)])
+def test_host_buffer_entry_point_row_blocks(pkg, M, n_keep):
+    """With M >= 2048 the host-buffer call moves A in and C out in row blocks (the last
+    one ragged here) while other blocks are multiplied; the result agrees with the resident path's (not
+    bit for bit: a row block may be scheduled with other k splits than the whole matrix), and
+    a second call on the same thread reuses streams and events."""
+    p = pkg.formats.make_random(M, 256, 1024, n_keep, seed=72)
+    op = pkg.NMSpMM.from_problem(p)
+    want = op.matmul(torch.from_numpy(p.A_km).cuda()).cpu().numpy()
+    d = pkg.make_desc(p.M, p.N, p.K, n_keep, pkg.format_of(n_keep), 128)
+    for _ in range(2):
+        C = np.full((p.M, p.N), np.nan, dtype=np.float32)
+        pkg.gemm_host(d, p.A_km, p.BT, p.DT, C)
+        assert rel_err(C, want) <= 1e-6
+    assert pkg.device_status() == 0
+
+
 def test_workspace_too_small_and_bad_pointers(pkg):
     p = pkg.formats.make_random(128, 256, 1024, 16, seed=71)
     op = pkg.NMSpMM.from_problem(p)
