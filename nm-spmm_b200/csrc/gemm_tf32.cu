@@ -1,20 +1,24 @@
 // TF32 tensor-core path of the vector-wise N:M sparse GEMM (tcgen05, accumulators in TMEM).
 //
-// One CTA computes a 128 x 256 tile of C (eight 32-column vectors) over all k windows.
+// One CTA computes a 128 x NS tile of C (NS / 32 vectors of 32 columns) over all k windows.
 // The dense contraction here is per vector: C[128 x 32] += A_gathered[128 x WS] . B[WS x 32],
 // and A_gathered differs for every vector, so the gather cannot be expressed by a shared-
 // memory descriptor.  It is done on chip instead:
 //   warp 0      TMA producer: per window one tiled copy of the dense A window (As[KS][128],
-//               unswizzled), one swizzled tiled copy per vector of its WS x 32
-//               block of B (32-byte chunks swizzled within 128-byte rows: the one legal
-//               layout of an MN-major TF32 operand), bulk copies of the packed indices and column_info lists.
-//   warps 2-9   two sets of four gather warps that take the vectors in turn.  Thread = row
-//               of the tile.  For one vector and window a thread reads its row's WS gathered
-//               values from As (conflict-free: consecutive lanes, consecutive words) and
-//               stores them as WS TMEM columns (tcgen05.st): the A operand of WS/8 MMAs.
-//   warp 1      one thread issues tcgen05.mma kind::tf32, M128 N32 K8, A from TMEM, B from
-//               shared memory, D = the vector's 32 accumulator columns in TMEM, and commits
-//               to mbarriers that hand the A buffers and the stage back.
+//               unswizzled), one swizzled tiled copy per vector of its WS x 32 block of B
+//               (32-byte chunks swizzled within 128-byte rows: the one legal layout of an
+//               MN-major TF32 operand), bulk copies of the packed indices and column lists.
+//   warps 2-17  sixteen gather warps, four (one per TMEM lane quadrant) for each vector of the
+//               window.  Thread = row of the tile.  Lane p of a warp resolves the vector's
+//               p-th index to a row of As; the offsets go round by shuffle; every thread
+//               reads its row's WS gathered values from As (conflict-free: consecutive lanes,
+//               consecutive words) and stores them as WS TMEM columns with one tcgen05.st
+//               per 16: the A operand of WS / 8 MMAs.  All vectors of a window share one
+//               A buffer in TMEM and one hand-off; the buffers form a ring.
+//   warp 1      one elected thread issues the window's tcgen05.mma kind::tf32 (M128 N32 K8,
+//               A from TMEM, B from shared memory, D = the vector's 32 accumulator columns)
+//               back to back and commits to the mbarriers that hand the A buffer and the
+//               stage back.
 //   epilogue    the gather warps read the accumulators (tcgen05.ld) and store C.
 // Every wait is bounded; a wait that gives up raises the device status word.
 #include <cuda.h>
@@ -32,42 +36,63 @@ struct Tf32Cfg {
     static constexpr int KS = KS_;
     static constexpr int G = WS / 8;                       // MMAs (K = 8 each) per vector and window
     static_assert(WS % 8 == 0, "kind::tf32 contracts 8 rows per instruction");
+    static constexpr int CH = WS < 16 ? WS : 16;           // TMEM columns per tcgen05.st
+    static constexpr int NCH = WS / CH;
+    static_assert(WS % CH == 0, "whole stores");
     static constexpr int B_BYTES = QT * WS * 128;          // per vector WS rows of 128 bytes, swizzled; multiple of 1024
     static constexpr int A_BYTES = KS * MS * 4;
     static constexpr int D_BYTES = ((WS * (QT > 4 ? QT : 4) * 4 + 127) / 128) * 128;
     static constexpr int CI_BYTES = (MODE == kModeHigh) ? QT * 256 : 0;
     static constexpr int STAGE_BYTES = ((B_BYTES + A_BYTES + D_BYTES + CI_BYTES + 1023) / 1024) * 1024;
     static constexpr int CTAS_PER_SM = (QT == 8) ? 1 : 2;
-    static constexpr int ST0 = ((CTAS_PER_SM == 1 ? 196 : 100) * 1024) / STAGE_BYTES;
+    static constexpr int ST0 = ((CTAS_PER_SM == 1 ? 216 : 108) * 1024) / STAGE_BYTES;
     static constexpr int STAGES = ST0 > 4 ? 4 : (ST0 < 2 ? 2 : ST0);
     static constexpr int TMEM_COLS = 512 / CTAS_PER_SM;    // each resident CTA allocates its share
-    static constexpr int NB0 = (TMEM_COLS - NS) / (2 * WS);
-    static constexpr int NB = NB0 > 4 ? 4 : NB0;           // A buffers (WS TMEM columns each) per gather set
-    static constexpr int GATHER_WARPS = 8;
+    static constexpr int BUF_COLS = QT * WS;               // one A buffer: every vector of one window
+    static constexpr int NBUF0 = (TMEM_COLS - NS) / BUF_COLS;
+    static constexpr int NBUF = NBUF0 > 4 ? 4 : NBUF0;     // ring of A buffers beside the accumulators
+    static_assert(NBUF >= 1, "no room for an A buffer beside the accumulators");
+    static constexpr int GATHER_WARPS = 16;
+    static constexpr int VPW = QT / 4;                     // vectors each gather warp carries per window
     static constexpr int THREADS = (2 + GATHER_WARPS) * 32;
-    static constexpr int TAB_BYTES = GATHER_WARPS * QT * WS * 4;   // per-warp table of gather offsets
-    static constexpr int NBARS = 2 * STAGES + 4 * NB + 1;
+    static constexpr int NBARS = 2 * STAGES + 2 * NBUF + 1;
     static constexpr int CTRL_BYTES = ((NBARS * 8 + 16 + 127) / 128) * 128;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + TAB_BYTES + CTRL_BYTES + 1024;   // + alignment slack
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + CTRL_BYTES + 1024;   // + alignment slack
     static constexpr int ACOL0 = NS;                       // first A-buffer column
-    static_assert(NB >= 1 && NS + 2 * NB * WS <= TMEM_COLS, "A buffers do not fit beside the accumulators");
     static constexpr bool HALF = false;
 };
+
+// Whole warp: each thread stores CH (8 or 16) consecutive 32-bit columns of its own lane.
+template <int CH>
+__device__ __forceinline__ void tmem_st_chunk(uint32_t taddr, const uint32_t (&v)[CH])
+{
+    if constexpr (CH == 8) {
+        tmem_st_x8(taddr, v);
+    } else {
+        static_assert(CH == 16, "8 or 16 columns per store");
+        asm volatile(
+            "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+            "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+            ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+              "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+            : "memory");
+    }
+}
 
 template <int WS, int KS_, int MODE, int QT_>
 __global__ void __launch_bounds__((Tf32Cfg<WS, KS_, MODE, QT_>::THREADS), (Tf32Cfg<WS, KS_, MODE, QT_>::CTAS_PER_SM))
 nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b)
 {
     using Cfg = Tf32Cfg<WS, KS_, MODE, QT_>;
-    constexpr int MS = Cfg::MS, NS = Cfg::NS, QT = Cfg::QT, KS = Cfg::KS, G = Cfg::G, STAGES = Cfg::STAGES, NB = Cfg::NB;
+    constexpr int MS = Cfg::MS, NS = Cfg::NS, QT = Cfg::QT, KS = Cfg::KS, G = Cfg::G, STAGES = Cfg::STAGES, NBUF = Cfg::NBUF;
+    constexpr int CH = Cfg::CH, NCH = Cfg::NCH, VPW = Cfg::VPW;
 
     extern __shared__ unsigned char smem_raw[];
     const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;          // swizzle atoms want 1024-byte alignment
-    const uint32_t tabs = ring + STAGES * Cfg::STAGE_BYTES;
-    const uint32_t bars = tabs + Cfg::TAB_BYTES;
+    const uint32_t bars = ring + STAGES * Cfg::STAGE_BYTES;
     const uint32_t bar_full = bars, bar_empty = bars + STAGES * 8;
-    const uint32_t bar_aready = bar_empty + STAGES * 8, bar_afree = bar_aready + 2 * NB * 8;
-    const uint32_t bar_acc = bar_afree + 2 * NB * 8;
+    const uint32_t bar_aready = bar_empty + STAGES * 8, bar_afree = bar_aready + NBUF * 8;
+    const uint32_t bar_acc = bar_afree + NBUF * 8;
     const uint32_t tmem_word = bar_acc + 8, abort_word = tmem_word + 4;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -85,10 +110,10 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full + s * 8, 1);
-            mbar_init(bar_empty + s * 8, Cfg::GATHER_WARPS + 1);          // eight gather warps + the MMA commit
+            mbar_init(bar_empty + s * 8, Cfg::GATHER_WARPS + 1);          // the gather warps + the MMA commit
         }
-        for (int b = 0; b < 2 * NB; ++b) {
-            mbar_init(bar_aready + b * 8, 4);                             // the four warps of a set
+        for (int b = 0; b < NBUF; ++b) {
+            mbar_init(bar_aready + b * 8, Cfg::GATHER_WARPS);
             mbar_init(bar_afree + b * 8, 1);                              // the MMA commit
         }
         mbar_init(bar_acc, 1);
@@ -114,112 +139,107 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
             }
             const uint32_t st = ring + s * Cfg::STAGE_BYTES, full = bar_full + s * 8;
             const uint32_t as = st + Cfg::B_BYTES, ds = as + Cfg::A_BYTES;
-            if (lane == 0) {
+            if (elect_one()) {
                 mbar_arrive_expect_tx(full, Cfg::A_BYTES + live_vecs * (WS * 128) +
                                                 nlb * (d_bytes + (MODE == kModeHigh ? 256u : 0u)));
+                for (int b = 0; b < nlb; ++b) {            // the indices first: the gather starts from them
+                    const int* src = g.D + ((static_cast<size_t>(lb0 + b) * g.W) << qs_shift) + static_cast<size_t>(it) * d_chunk;
+                    bulk_g2s(ds + b * d_bytes, src, d_bytes, full);
+                    if (MODE == kModeHigh) {
+                        const int* ci = g.cinfo + (static_cast<size_t>(lb0 + b) * n_win + it) * 64;
+                        bulk_g2s(ds + Cfg::D_BYTES + b * 256, ci, 256, full);
+                    }
+                }
                 tma_load_2d(as, &map_a, bi, it * KS, full);
+                for (int v = 0; v < live_vecs; ++v) tma_load_2d(st + v * (WS * 128), &map_b, bj + v * 32, it * WS, full);
             }
             __syncwarp();
-            if (lane < live_vecs) tma_load_2d(st + lane * (WS * 128), &map_b, bj + lane * 32, it * WS, full);
-            if (lane < nlb) {
-                const int* src = g.D + ((static_cast<size_t>(lb0 + lane) * g.W) << qs_shift) + static_cast<size_t>(it) * d_chunk;
-                bulk_g2s(ds + lane * d_bytes, src, d_bytes, full);
-                if (MODE == kModeHigh) {
-                    const int* ci = g.cinfo + (static_cast<size_t>(lb0 + lane) * n_win + it) * 64;
-                    bulk_g2s(ds + Cfg::D_BYTES + lane * 256, ci, 256, full);
-                }
-            }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         constexpr uint32_t idesc = umma_idesc_tf32(128, 32);
-        unsigned cnt0 = 0u, cnt1 = 0u;                     // units issued per gather set
         bool alive = true;
-        for (int it = 0; it < n_win && alive; ++it) {
-            const int s = it % STAGES;
+        for (int it = 0; it < n_win; ++it) {
+            const int s = it % STAGES, b = it % NBUF;
             bool ok = mbar_wait_bounded(bar_full + s * 8, (it / STAGES) & 1, abort_word);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) { alive = false; break; }
-            const uint32_t st = ring + s * Cfg::STAGE_BYTES;
-            int set = 0;
-            for (int v = 0; v < live_vecs && alive; ++v) {
-                // one chunk = the whole window of one vector: G MMAs on one A buffer
-                const unsigned c = set ? cnt1 : cnt0;
-                const int buf = set * NB + static_cast<int>(c % NB);
-                ok = mbar_spin_bounded(bar_aready + buf * 8, (c / NB) & 1, abort_word);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) { alive = false; break; }
-                tc_fence_after_sync();
-                if (lane == 0) {
+            ok = ok && mbar_spin_bounded(bar_aready + b * 8, (it / NBUF) & 1, abort_word);
+            if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+            tc_fence_after_sync();
+            if (elect_one()) {
+                const uint32_t st = ring + s * Cfg::STAGE_BYTES;
+                const uint32_t abuf = tmem_addr(tmem, 0, Cfg::ACOL0 + b * Cfg::BUF_COLS);
+                for (int v = 0; v < live_vecs; ++v) {
 #pragma unroll
                     for (int gi = 0; gi < G; ++gi)
-                        umma_tf32_ts(tmem_addr(tmem, 0, v * 32), tmem_addr(tmem, 0, Cfg::ACOL0 + buf * WS + gi * 8),
+                        umma_tf32_ts(tmem_addr(tmem, 0, v * 32), abuf + v * WS + gi * 8,
                                      umma_desc_mn_tf32(st + v * (WS * 128) + gi * 1024), idesc, (it | gi) != 0);
-                    tc_commit(bar_afree + buf * 8);        // the A buffer is free once these MMAs have read it
                 }
-                __syncwarp();
-                if (set) ++cnt1; else ++cnt0;
-                set ^= 1;
+                tc_commit(bar_afree + b * 8);              // the A buffer is free once these MMAs have read it
+                tc_commit(bar_empty + s * 8);              // and so are the window's B blocks
             }
-            if (lane == 0) tc_commit(bar_empty + s * 8);   // the window's B blocks have been read
             __syncwarp();
         }
         if (!alive && lane == 0) atomicMax(g.status, kDevTimeoutMma);
-        if (lane == 0) tc_commit(bar_acc);                 // every MMA has completed: accumulators are final
+        if (elect_one()) tc_commit(bar_acc);               // every MMA has completed: accumulators are final
         __syncwarp();
     } else {
         // ------------------------------------------------------------------ gather warps
-        const int gw = warp - 2;                           // 0..7
-        const int set = gw >> 2;                           // which set of four warps
+        const int gw = warp - 2;                           // 0..15
         const int quad = warp & 3;                         // TMEM lane quadrant this warp may touch
         const int row = quad * 32 + lane;                  // row of the tile this thread carries
-        const uint32_t tab = tabs + gw * (QT * WS * 4);
-        unsigned cnt = 0;                                  // units this set has produced
-        bool alive = true;
-        for (int it = 0; it < n_win && alive; ++it) {
-            const int s = it % STAGES;
-            bool ok = mbar_wait_bounded(bar_full + s * 8, (it / STAGES) & 1, abort_word);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) { alive = false; break; }
-            const uint32_t st = ring + s * Cfg::STAGE_BYTES;
-            const uint32_t as = st + Cfg::B_BYTES, ds = as + Cfg::A_BYTES, cs = ds + Cfg::D_BYTES;
-            // Resolve the window's indices to byte offsets of rows of As, once per warp.
-            for (int e = lane; e < live_vecs * WS; e += 32) {
-                const int v = e / WS, p = e - v * WS;
-                const int q = (bj >> 5) + v;
-                const int lb = (q >> qs_shift) - lb0;
-                int k = lds_s32(ds + (lb * d_chunk + (p << qs_shift) + (q & ((1 << qs_shift) - 1))) * 4);
-                if (MODE == kModeHigh) k = lds_s32(cs + (lb * 64 + k) * 4);
-                sts_volatile_s32(tab + e * 4, k * (MS * 4));
-            }
-            __syncwarp();
-            for (int v = set; v < live_vecs && alive; v += 2) {     // the two sets take the vectors in turn
-                const int buf = set * NB + static_cast<int>(cnt % NB);
-                if (cnt >= NB) {
-                    ok = mbar_spin_bounded(bar_afree + buf * 8, ((cnt / NB) - 1) & 1, abort_word);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) { alive = false; break; }
-                    tc_fence_after_sync();
-                }
-                const uint32_t base = as + row * 4;
+        const int v0 = gw >> 2;                            // its vectors: v0, v0 + 4, ...
+        // where lane p finds index p of vector v0 + 4 i within the staged index block
+        uint32_t d_rel[VPW], ci_rel[VPW];
 #pragma unroll
-                for (int gi = 0; gi < G; ++gi) {
-                    const int4 o0 = lds_i4(tab + (v * WS + gi * 8) * 4), o1 = lds_i4(tab + (v * WS + gi * 8 + 4) * 4);
-                    uint32_t a[8];
-                    a[0] = lds_u32(base + o0.x); a[1] = lds_u32(base + o0.y);
-                    a[2] = lds_u32(base + o0.z); a[3] = lds_u32(base + o0.w);
-                    a[4] = lds_u32(base + o1.x); a[5] = lds_u32(base + o1.y);
-                    a[6] = lds_u32(base + o1.z); a[7] = lds_u32(base + o1.w);
-                    tmem_st_x8(tmem_addr(tmem, quad * 32, Cfg::ACOL0 + buf * WS + gi * 8), a);
+        for (int i = 0; i < VPW; ++i) {
+            const int q = (bj >> 5) + v0 + 4 * i;
+            const int lb = (q >> qs_shift) - lb0;
+            d_rel[i] = static_cast<uint32_t>(lb * d_chunk + (lane << qs_shift) + (q & ((1 << qs_shift) - 1))) * 4u;
+            ci_rel[i] = static_cast<uint32_t>(lb * 256);
+        }
+        bool alive = true;
+        for (int it = 0; it < n_win; ++it) {
+            const int s = it % STAGES, b = it % NBUF;
+            bool ok = mbar_wait_bounded(bar_full + s * 8, (it / STAGES) & 1, abort_word);
+            if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+            const uint32_t st = ring + s * Cfg::STAGE_BYTES;
+            const uint32_t as = st + Cfg::B_BYTES + row * 4, ds = st + Cfg::B_BYTES + Cfg::A_BYTES, cs = ds + Cfg::D_BYTES;
+            // lane p resolves index p of each of the warp's vectors to a byte offset into As
+            uint32_t off[VPW];
+#pragma unroll
+            for (int i = 0; i < VPW; ++i) {
+                int k = 0;
+                if (lane < WS && v0 + 4 * i < live_vecs) {
+                    k = lds_s32(ds + d_rel[i]);
+                    if (MODE == kModeHigh) k = lds_s32(cs + ci_rel[i] + k * 4);
                 }
-                tmem_wait_st();
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_aready + buf * 8);
-                ++cnt;
+                off[i] = static_cast<uint32_t>(k) * (MS * 4);
             }
+            if (it >= NBUF) {
+                ok = mbar_wait_bounded(bar_afree + b * 8, ((it / NBUF) - 1) & 1, abort_word);
+                if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+                tc_fence_after_sync();
+            }
+#pragma unroll
+            for (int i = 0; i < VPW; ++i) {
+                const int v = v0 + 4 * i;
+                if (v < live_vecs) {                       // warp-uniform
+#pragma unroll
+                    for (int c = 0; c < NCH; ++c) {
+                        uint32_t a[CH];
+#pragma unroll
+                        for (int j = 0; j < CH; ++j) a[j] = lds_u32(as + __shfl_sync(0xffffffffu, off[i], c * CH + j));
+                        tmem_st_chunk<CH>(tmem_addr(tmem, quad * 32, Cfg::ACOL0 + b * Cfg::BUF_COLS + v * WS + c * CH), a);
+                    }
+                }
+            }
+            tmem_wait_st();
+            tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_empty + s * 8);     // this warp has finished reading As of the stage
+            if (lane == 0) {
+                mbar_arrive(bar_aready + b * 8);
+                mbar_arrive(bar_empty + s * 8);            // this warp has finished reading As of the stage
+            }
         }
         // ------------------------------------------------------------------ epilogue
         bool ok = alive && mbar_wait_bounded(bar_acc, 0, abort_word);
@@ -227,10 +247,9 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
         if (ok) {
             tc_fence_after_sync();
             const int r = bi + row;
-            const int half = gw >> 2;                      // lower or upper half of the tile's columns
 #pragma unroll 1
-            for (int c = 0; c < QT / 2; ++c) {
-                const int col = half * (NS / 2) + c * 32;
+            for (int i = 0; i < VPW; ++i) {
+                const int col = (v0 + 4 * i) * 32;
                 if (col >= live_vecs * 32) break;
                 uint32_t v[32];
                 tmem_ld_x32(tmem_addr(tmem, quad * 32, col), v);
