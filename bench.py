@@ -357,10 +357,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             tf, tm = uf / (tf32_peak * 1e12), algorithmic_bytes(M, n_local, K, n_keep) / (hbm_gbs * 1e9)
             exact = opr.matmul(A_sets[0])
             err = float((opr.matmul(A_sets[0], path=pkg.PATH_TF32) - exact).norm() / exact.norm())
+            info = pkg.plan(opr.desc(M, path=pkg.PATH_TF32))
             rows.append({"n_keep": n_keep, "path": "tf32", "ms": t, "useful_tflops": uf / (t * 1e-3) / 1e12,
                          "dense_equivalent_tflops": 2.0 * M * n_local * K / (t * 1e-3) / 1e12,
-                         "roofline_frac": max(tf, tm) / (t * 1e-3), "rel_err_vs_fp32_path": err})
-        tf32 = {"kernel": "nm_gemm_tf32_kernel, tile 128x128, tcgen05.mma kind::tf32 M128 N32 K8, A gathered into TMEM",
+                         "roofline_frac": max(tf, tm) / (t * 1e-3), "rel_err_vs_fp32_path": err,
+                         "tile": [info.tile_m, info.tile_n]})
+        tf32 = {"kernel": "nm_gemm_tf32_kernel, tcgen05.mma kind::tf32 M128 N32 K8, A gathered into TMEM per vector",
                 "bound": "tensor", "peak": tf32_peak, "unit": "TFLOP/s",
                 "peak_source": "half of the measured dense bf16 rate in MEASURED_PEAKS.json (burst)"
                                if "bf16_tflops" in peaks else "half of the fallback 1590 TFLOP/s bf16",

@@ -128,16 +128,21 @@ static int make_plan(const nmspmm_gemm_desc* d, int sms, Plan* p)
     if (rc != NMSPMM_OK) return rc;
     if (sms <= 0) sms = 148;
     if (d->path == NMSPMM_PATH_TF32) {
-        // Tensor-core path: one 128 x 256 tile per CTA over all k windows (split_k is ignored).
-        // tile 128 x 128 (two CTAs per SM cover each other's hand-off latencies) unless
-        // the caller asks for the 128 x 256 tile
-        const int want_ns = (d->tile == kTile128x256) ? 256 : 128;
+        // Tensor-core path: one tile per CTA over all k windows (split_k is ignored).  Tile
+        // 128 x 256 with one CTA per SM is the faster one for the 64-k window formats once
+        // it fills the GPU (measured at 4096^3: 0.233 against 0.266 ms at 8:32, 0.166 against
+        // 0.232 ms at 4:32), tile 128 x 128 with two CTAs per SM for the 32-k window formats
+        // (0.360 against 0.424 ms at 16:32); the caller's tile wins over both.
+        int want_ns = (mode == kModeHigh && ((d->N + 255) / 256) * ((d->M + 127) / 128) >= sms) ? 256 : 128;
+        if (d->tile == kTile128x256) want_ns = 256;
+        if (d->tile == kTile128x128) want_ns = 128;
         for (int i = 0; i < kTf32VariantCount; ++i)
             if (kTf32Variants[i].n_keep == d->n_keep && kTf32Variants[i].mode == mode && kTf32Variants[i].ns == want_ns)
                 p->tv = &kTf32Variants[i];
         if (!p->tv) return NMSPMM_UNSUPPORTED;
         p->ws = p->tv->ws;
         p->W = d->K / 32 * d->n_keep;
+        if (p->W % p->ws != 0) return NMSPMM_UNSUPPORTED;   // 12:32 is staged as window pairs: K % 64 == 0
         p->n_win = p->W / p->ws;
         p->tiles_x = (d->N + p->tv->ns - 1) / p->tv->ns;
         p->tiles_y = (d->M + 127) / 128;

@@ -8,8 +8,10 @@
 //               unswizzled), one swizzled tiled copy per vector of its WS x 32 block of B
 //               (32-byte chunks swizzled within 128-byte rows: the one legal layout of an
 //               MN-major TF32 operand), bulk copies of the packed indices and column lists.
-//   warps 2-17  sixteen gather warps, four (one per TMEM lane quadrant) for each vector of the
-//               window.  Thread = row of the tile.  Lane p of a warp resolves the vector's
+//   warps 2-17  sixteen gather warps in two groups that take the windows in turn (one group's
+//               waits overlap the other's copying, which keeps shared memory busy); within
+//               a group four warps (one per TMEM lane quadrant) work on one vector.  Thread
+//               = row of the tile.  Lane p of a warp resolves the vector's
 //               p-th index to a row of As; the offsets go round by shuffle; every thread
 //               reads its row's WS gathered values from As (conflict-free: consecutive lanes,
 //               consecutive words) and stores them as WS TMEM columns with one tcgen05.st
@@ -30,13 +32,30 @@
 
 namespace nmspmm {
 
+// Diagnostic build (-DNMSPMM_PROFILE_WAITS): the first gather warp and the MMA warp of every
+// CTA add up the cycles they spend in each phase.
+#ifdef NMSPMM_PROFILE_WAITS
+__device__ unsigned long long g_tf32_profile[16];
+#define TF_DECL(...) long long __VA_ARGS__
+#define TF_T(name) const long long name = clock64()
+#define TF_ADD(acc, since) acc += clock64() - (since)
+#define TF_OUT(i, v) atomicAdd(&g_tf32_profile[i], (unsigned long long)(v))
+#else
+#define TF_DECL(...)
+#define TF_T(name)
+#define TF_ADD(acc, since)
+#define TF_OUT(i, v)
+#endif
+
 template <int WS, int KS_, int MODE, int QT_>
 struct Tf32Cfg {
     static constexpr int MS = 128, QT = QT_, NS = QT * 32;   // QT = 8: one CTA per SM; QT = 4: two
     static constexpr int KS = KS_;
     static constexpr int G = WS / 8;                       // MMAs (K = 8 each) per vector and window
     static_assert(WS % 8 == 0, "kind::tf32 contracts 8 rows per instruction");
-    static constexpr int CH = WS < 16 ? WS : 16;           // TMEM columns per tcgen05.st
+    // 12:32 is staged as pairs of 32-k windows (24 kept rows, three MMAs): PAIR.
+    static constexpr bool PAIR = (MODE == kModeLow && KS == 64);
+    static constexpr int CH = (WS % 16 == 0) ? 16 : 8;     // TMEM columns per tcgen05.st
     static constexpr int NCH = WS / CH;
     static_assert(WS % CH == 0, "whole stores");
     static constexpr int B_BYTES = QT * WS * 128;          // per vector WS rows of 128 bytes, swizzled; multiple of 1024
@@ -46,14 +65,23 @@ struct Tf32Cfg {
     static constexpr int STAGE_BYTES = ((B_BYTES + A_BYTES + D_BYTES + CI_BYTES + 1023) / 1024) * 1024;
     static constexpr int CTAS_PER_SM = (QT == 8) ? 1 : 2;
     static constexpr int ST0 = ((CTAS_PER_SM == 1 ? 216 : 108) * 1024) / STAGE_BYTES;
-    static constexpr int STAGES = ST0 > 4 ? 4 : (ST0 < 2 ? 2 : ST0);
+    static constexpr int STAGES = ST0 >= 4 ? 4 : 2;        // even: a stage always serves the same group of gather warps
     static constexpr int TMEM_COLS = 512 / CTAS_PER_SM;    // each resident CTA allocates its share
     static constexpr int BUF_COLS = QT * WS;               // one A buffer: every vector of one window
     static constexpr int NBUF0 = (TMEM_COLS - NS) / BUF_COLS;
     static constexpr int NBUF = NBUF0 > 4 ? 4 : NBUF0;     // ring of A buffers beside the accumulators
     static_assert(NBUF >= 1, "no room for an A buffer beside the accumulators");
     static constexpr int GATHER_WARPS = 16;
-    static constexpr int VPW = QT / 4;                     // vectors each gather warp carries per window
+    // Groups of gather warps that take the windows in turn.  A warp's waits on one mbarrier
+    // must follow one another phase by phase (a waiter two phases ahead would see the
+    // parity it expects too early), so every A buffer and every stage has to stay with one
+    // group: two groups only when both ring depths are even.
+    static constexpr int GROUPS = (NBUF % 2 == 0 && STAGES % 2 == 0) ? 2 : 1;
+    static constexpr int GROUP_WARPS = GATHER_WARPS / GROUPS;
+    static constexpr int VSTEP = GROUP_WARPS / 4;          // vectors a group gathers at a time
+    static constexpr int VPW = QT / VSTEP;                 // vectors each gather warp carries per window
+    static_assert(GROUP_WARPS % 4 == 0 && QT % VSTEP == 0, "four warps (TMEM lane quadrants) per vector");
+    static_assert(VPW % GROUPS == 0, "the epilogue shares each warp's vectors out among the groups");
     static constexpr int THREADS = (2 + GATHER_WARPS) * 32;
     static constexpr int NBARS = 2 * STAGES + 2 * NBUF + 1;
     static constexpr int CTRL_BYTES = ((NBARS * 8 + 16 + 127) / 128) * 128;
@@ -110,10 +138,10 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full + s * 8, 1);
-            mbar_init(bar_empty + s * 8, Cfg::GATHER_WARPS + 1);          // the gather warps + the MMA commit
+            mbar_init(bar_empty + s * 8, Cfg::GROUP_WARPS + 1);           // the window's gather warps + the MMA commit
         }
         for (int b = 0; b < NBUF; ++b) {
-            mbar_init(bar_aready + b * 8, Cfg::GATHER_WARPS);
+            mbar_init(bar_aready + b * 8, Cfg::GROUP_WARPS);
             mbar_init(bar_afree + b * 8, 1);                              // the MMA commit
         }
         mbar_init(bar_acc, 1);
@@ -159,11 +187,18 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
         // ------------------------------------------------------------------ MMA issuer
         constexpr uint32_t idesc = umma_idesc_tf32(128, 32);
         bool alive = true;
+        TF_DECL(m_full = 0, m_ready = 0, m_issue = 0);
+        TF_T(m_start);
         for (int it = 0; it < n_win; ++it) {
             const int s = it % STAGES, b = it % NBUF;
+            TF_T(t0);
             bool ok = mbar_wait_bounded(bar_full + s * 8, (it / STAGES) & 1, abort_word);
+            TF_ADD(m_full, t0);
+            TF_T(t1);
             ok = ok && mbar_spin_bounded(bar_aready + b * 8, (it / NBUF) & 1, abort_word);
             if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+            TF_ADD(m_ready, t1);
+            TF_T(t2);
             tc_fence_after_sync();
             if (elect_one()) {
                 const uint32_t st = ring + s * Cfg::STAGE_BYTES;
@@ -178,7 +213,11 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
                 tc_commit(bar_empty + s * 8);              // and so are the window's B blocks
             }
             __syncwarp();
+            TF_ADD(m_issue, t2);
         }
+#ifdef NMSPMM_PROFILE_WAITS
+        if (lane == 0) { TF_OUT(7, m_full); TF_OUT(8, m_ready); TF_OUT(9, m_issue); TF_OUT(10, clock64() - m_start); }
+#endif
         if (!alive && lane == 0) atomicMax(g.status, kDevTimeoutMma);
         if (elect_one()) tc_commit(bar_acc);               // every MMA has completed: accumulators are final
         __syncwarp();
@@ -187,21 +226,28 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
         const int gw = warp - 2;                           // 0..15
         const int quad = warp & 3;                         // TMEM lane quadrant this warp may touch
         const int row = quad * 32 + lane;                  // row of the tile this thread carries
-        const int v0 = gw >> 2;                            // its vectors: v0, v0 + 4, ...
+        const int grp = gw / Cfg::GROUP_WARPS;             // its windows: grp, grp + GROUPS, ...
+        const int v0 = (gw % Cfg::GROUP_WARPS) >> 2;       // its vectors: v0, v0 + VSTEP, ...
+        constexpr int VSTEP = Cfg::VSTEP;
         // where lane p finds index p of vector v0 + 4 i within the staged index block
         uint32_t d_rel[VPW], ci_rel[VPW];
 #pragma unroll
         for (int i = 0; i < VPW; ++i) {
-            const int q = (bj >> 5) + v0 + 4 * i;
+            const int q = (bj >> 5) + v0 + VSTEP * i;
             const int lb = (q >> qs_shift) - lb0;
             d_rel[i] = static_cast<uint32_t>(lb * d_chunk + (lane << qs_shift) + (q & ((1 << qs_shift) - 1))) * 4u;
             ci_rel[i] = static_cast<uint32_t>(lb * 256);
         }
         bool alive = true;
-        for (int it = 0; it < n_win; ++it) {
+        TF_DECL(g_full = 0, g_res = 0, g_free = 0, g_move = 0, g_done = 0);
+        TF_T(g_start);
+        for (int it = grp; it < n_win; it += Cfg::GROUPS) {
             const int s = it % STAGES, b = it % NBUF;
+            TF_T(t0);
             bool ok = mbar_wait_bounded(bar_full + s * 8, (it / STAGES) & 1, abort_word);
             if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+            TF_ADD(g_full, t0);
+            TF_T(t1);
             const uint32_t st = ring + s * Cfg::STAGE_BYTES;
             const uint32_t as = st + Cfg::B_BYTES + row * 4, ds = st + Cfg::B_BYTES + Cfg::A_BYTES, cs = ds + Cfg::D_BYTES;
             // lane p resolves index p of each of the warp's vectors to a byte offset into As
@@ -209,20 +255,25 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
             for (int i = 0; i < VPW; ++i) {
                 int k = 0;
-                if (lane < WS && v0 + 4 * i < live_vecs) {
+                if (lane < WS && v0 + VSTEP * i < live_vecs) {
                     k = lds_s32(ds + d_rel[i]);
                     if (MODE == kModeHigh) k = lds_s32(cs + ci_rel[i] + k * 4);
+                    if (Cfg::PAIR && lane >= WS / 2) k += 32;      // second window of the pair
                 }
                 off[i] = static_cast<uint32_t>(k) * (MS * 4);
             }
+            TF_ADD(g_res, t1);
+            TF_T(t2);
             if (it >= NBUF) {
                 ok = mbar_wait_bounded(bar_afree + b * 8, ((it / NBUF) - 1) & 1, abort_word);
                 if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
                 tc_fence_after_sync();
             }
+            TF_ADD(g_free, t2);
+            TF_T(t3);
 #pragma unroll
             for (int i = 0; i < VPW; ++i) {
-                const int v = v0 + 4 * i;
+                const int v = v0 + VSTEP * i;
                 if (v < live_vecs) {                       // warp-uniform
 #pragma unroll
                     for (int c = 0; c < NCH; ++c) {
@@ -233,6 +284,8 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
                     }
                 }
             }
+            TF_ADD(g_move, t3);
+            TF_T(t4);
             tmem_wait_st();
             tc_fence_before_sync();
             __syncwarp();
@@ -240,7 +293,14 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
                 mbar_arrive(bar_aready + b * 8);
                 mbar_arrive(bar_empty + s * 8);            // this warp has finished reading As of the stage
             }
+            TF_ADD(g_done, t4);
         }
+#ifdef NMSPMM_PROFILE_WAITS
+        if (gw == 0 && lane == 0) {
+            TF_OUT(0, g_full); TF_OUT(1, g_res); TF_OUT(2, g_free); TF_OUT(3, g_move); TF_OUT(4, g_done);
+            TF_OUT(5, clock64() - g_start); TF_OUT(6, 1);
+        }
+#endif
         // ------------------------------------------------------------------ epilogue
         bool ok = alive && mbar_wait_bounded(bar_acc, 0, abort_word);
         ok = __all_sync(0xffffffffu, ok);
@@ -248,8 +308,8 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
             tc_fence_after_sync();
             const int r = bi + row;
 #pragma unroll 1
-            for (int i = 0; i < VPW; ++i) {
-                const int col = (v0 + 4 * i) * 32;
+            for (int i = grp; i < VPW; i += Cfg::GROUPS) {  // the groups share the warp's vectors out
+                const int col = (v0 + VSTEP * i) * 32;
                 if (col >= live_vecs * 32) break;
                 uint32_t v[32];
                 tmem_ld_x32(tmem_addr(tmem, quad * 32, col), v);
@@ -304,10 +364,21 @@ static cudaError_t launch_tf32(const GemmArgs& a, int tiles, cudaStream_t st)
 extern const Tf32Variant kTf32Variants[] = {
     NMSPMM_TF32_VARIANT(32, 32, 32, kModeLow, 8),  NMSPMM_TF32_VARIANT(32, 32, 32, kModeLow, 4),
     NMSPMM_TF32_VARIANT(16, 16, 32, kModeLow, 8),  NMSPMM_TF32_VARIANT(16, 16, 32, kModeLow, 4),
+    NMSPMM_TF32_VARIANT(12, 24, 64, kModeLow, 8),  NMSPMM_TF32_VARIANT(12, 24, 64, kModeLow, 4),
     NMSPMM_TF32_VARIANT(8, 8, 32, kModeLow, 8),    NMSPMM_TF32_VARIANT(8, 8, 32, kModeLow, 4),
     NMSPMM_TF32_VARIANT(8, 16, 64, kModeHigh, 8),  NMSPMM_TF32_VARIANT(8, 16, 64, kModeHigh, 4),
     NMSPMM_TF32_VARIANT(4, 8, 64, kModeHigh, 8),   NMSPMM_TF32_VARIANT(4, 8, 64, kModeHigh, 4),
 };
 extern const int kTf32VariantCount = sizeof(kTf32Variants) / sizeof(kTf32Variants[0]);
+
+#ifdef NMSPMM_PROFILE_WAITS
+// Diagnostic build only: reads and clears the phase counters.
+extern "C" int nmspmm_debug_tf32_profile(unsigned long long* out16)
+{
+    if (cudaMemcpyFromSymbol(out16, g_tf32_profile, sizeof(unsigned long long) * 16) != cudaSuccess) return 1;
+    unsigned long long zero[16] = {};
+    return cudaMemcpyToSymbol(g_tf32_profile, zero, sizeof(zero)) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 }  // namespace nmspmm

@@ -19,28 +19,31 @@ def rel_err(got, want):
     return float(np.linalg.norm(got.astype(np.float64) - want) / np.linalg.norm(want))
 
 
-def run(pkg, p, layout_ns=128, fmt=None):
+def run(pkg, p, layout_ns=128, fmt=None, tile=0):
     op = pkg.NMSpMM.from_problem(p, layout_ns=layout_ns, fmt=fmt)
-    C = op.matmul(torch.from_numpy(p.A_km).cuda(), path=pkg.PATH_TF32)
+    C = op.matmul(torch.from_numpy(p.A_km).cuda(), path=pkg.PATH_TF32, tile=tile)
     torch.cuda.synchronize()
     assert pkg.device_status() == 0
     return C.cpu().numpy()
 
 
-@pytest.mark.parametrize("n_keep,fmt", [(16, 0), (32, 0), (8, 0), (8, 1), (4, 1)])
+@pytest.mark.parametrize("n_keep,fmt", [(16, 0), (12, 0), (32, 0), (8, 0), (8, 1), (4, 1)])
 @pytest.mark.parametrize("layout", [32, 64, 128])
-def test_tf32_every_supported_ratio_and_layout(pkg, orc, n_keep, fmt, layout):
+@pytest.mark.parametrize("tile", [1, 5])
+def test_tf32_every_supported_ratio_layout_and_tile(pkg, orc, n_keep, fmt, layout, tile):
+    """Tile 1 = 128 x 128 (two CTAs per SM), tile 5 = 128 x 256 (one)."""
     p = pkg.formats.make_random(256, 512, 512, n_keep, seed=200 + n_keep)
     want = orc.nm_gemm_f64(p.A_km, p.B_col, p.D_col)
-    err = rel_err(run(pkg, p, layout_ns=layout, fmt=fmt), want)
+    err = rel_err(run(pkg, p, layout_ns=layout, fmt=fmt, tile=tile), want)
     assert err <= TF32_TOL, err
 
 
 @pytest.mark.parametrize("M,N", [(200, 640), (16, 128), (128, 96), (392, 1056)])
-def test_tf32_ragged_rows_and_columns(pkg, orc, M, N):
-    p = pkg.formats.make_random(M, N, 256, 8, seed=210)
+@pytest.mark.parametrize("n_keep,tile", [(8, 1), (8, 5), (12, 1), (16, 5)])
+def test_tf32_ragged_rows_and_columns(pkg, orc, M, N, n_keep, tile):
+    p = pkg.formats.make_random(M, N, 256, n_keep, seed=210)
     want = orc.nm_gemm_f64(p.A_km, p.B_col, p.D_col)
-    assert rel_err(run(pkg, p, layout_ns=32), want) <= TF32_TOL
+    assert rel_err(run(pkg, p, layout_ns=32, tile=tile), want) <= TF32_TOL
 
 
 def test_tf32_single_window(pkg, orc):
@@ -59,15 +62,16 @@ def test_tf32_is_deterministic_and_close_to_the_exact_path(pkg):
     assert float((a - exact).norm() / exact.norm()) <= TF32_TOL
 
 
-def test_tf32_unsupported_ratio_is_refused(pkg):
-    p = pkg.formats.make_random(128, 256, 256, 12, seed=213)
+def test_tf32_refuses_12_of_32_with_an_odd_number_of_windows(pkg):
+    """12:32 runs as pairs of 32-k windows (24 kept rows = three K=8 instructions)."""
+    p = pkg.formats.make_random(128, 256, 96, 12, seed=213)
     op = pkg.NMSpMM.from_problem(p)
     with pytest.raises(pkg.NMSpMMError) as e:
         op.matmul(torch.from_numpy(p.A_km).cuda(), path=pkg.PATH_TF32)
     assert e.value.status == pkg.UNSUPPORTED
 
 
-@pytest.mark.parametrize("n_keep", [16, 8, 4])
+@pytest.mark.parametrize("n_keep", [16, 12, 8, 4])
 def test_tf32_square_4096_full_size(pkg, orc, n_keep):
     p = pkg.formats.make_random(4096, 4096, 4096, n_keep, seed=80)
     op = pkg.NMSpMM.from_problem(p)
