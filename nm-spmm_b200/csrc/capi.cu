@@ -52,7 +52,7 @@ static DeviceInfo g_dev[64];
 static std::mutex g_dev_mutex;
 __device__ int g_status_word;      // raised by kernels whose bounded waits gave up
 #ifdef NMSPMM_PROFILE_WAITS
-__device__ unsigned long long g_wait_profile[4];   // diagnostic build: wait, fill, total cycles of warp 0, CTA count
+__device__ unsigned long long g_wait_profile[8];   // diagnostic build: wait, fill, total cycles of warp 0, CTA count, epilogue sum / max, total max
 #endif
 
 static int device_info(DeviceInfo** out)
@@ -87,8 +87,15 @@ struct Plan {
     int n_virtual = 0;      // unit ranges (= CTAs)
     int slots = 0;          // scratch slots for tile pieces
     int grid = 0;           // resident CTAs launched
+    bool deferred = false;  // many pieces per tile: a second kernel adds them (else the last piece to arrive does)
+    int first_split_tile = 0, n_split_tiles = 0;
     size_t counters_bytes = 0, partial_bytes = 0;
 };
+
+// Pieces per tile from which the reduction moves out of the multiply into its own
+// kernel.  One CTA adding p pieces walks them one after the other (about 1.5 us per piece
+// of a 128 x 128 tile); the kernel spreads that over the GPU for one launch (2-3 us).
+constexpr int kDeferPieces = 4;
 
 static int check_desc(const nmspmm_gemm_desc* d, int* mode_out)
 {
@@ -176,6 +183,9 @@ static int make_plan(const nmspmm_gemm_desc* d, int sms, Plan* p)
         p->split_k = s;
         p->n_virtual = static_cast<int>(n_tiles * s);
         p->slots = (s > 1) ? p->n_virtual : 0;
+        p->deferred = s > kDeferPieces;
+        p->first_split_tile = 0;
+        p->n_split_tiles = p->n_tiles;
     } else {
         // Automatic: whole tiles for as many complete waves of resident CTAs as there are,
         // then the units of the remaining tiles in equal ranges, one per resident CTA, each
@@ -200,6 +210,9 @@ static int make_plan(const nmspmm_gemm_desc* d, int sms, Plan* p)
         // equal ranges that coincide with whole tiles need no scratch
         const bool aligned = (n_sk == 0) || (n_sk == tail_tiles);
         p->slots = aligned ? 0 : static_cast<int>(2 * n_sk);
+        p->deferred = !aligned && n_sk > static_cast<long long>(kDeferPieces - 1) * tail_tiles;   // a tile sees up to n_sk / tail_tiles + 1 pieces
+        p->first_split_tile = p->n_dp;
+        p->n_split_tiles = static_cast<int>(tail_tiles);
     }
     p->grid = p->n_virtual;      // one unit range per CTA (the automatic schedule never exceeds the resident count)
     if (p->slots > 0) {
@@ -477,11 +490,13 @@ int nmspmm_gemm(const nmspmm_gemm_desc* desc, const float* A_dev, const float* B
     if (p.slots > 0) {
         if (!workspace_dev || !aligned16(workspace_dev)) return NMSPMM_INVALID_ARGUMENT;
         if (workspace_bytes < p.counters_bytes + p.partial_bytes) return NMSPMM_WORKSPACE_TOO_SMALL;
-        a.counters = static_cast<unsigned*>(workspace_dev);
+        a.counters = p.deferred ? nullptr : static_cast<unsigned*>(workspace_dev);
         a.partial = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace_dev) + p.counters_bytes);
     }
     cudaError_t e = p.v ? p.v->launch(a, p.grid, static_cast<cudaStream_t>(stream))
                         : p.tv->launch(a, p.grid, static_cast<cudaStream_t>(stream));
+    if (e == cudaSuccess && p.v && p.slots > 0 && p.deferred)
+        e = launch_reduce_pieces(p.v->tile_id, a, p.first_split_tile, p.n_split_tiles, static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? NMSPMM_OK : cuda_fail(e);
 }
 
@@ -659,11 +674,11 @@ int nmspmm_gemm_host(const nmspmm_gemm_desc* desc, const float* A_host, const fl
 
 #ifdef NMSPMM_PROFILE_WAITS
 // Diagnostic build only: reads and clears the cycle counters.
-int nmspmm_debug_wait_profile(unsigned long long* out4)
+int nmspmm_debug_wait_profile(unsigned long long* out8)
 {
-    cudaError_t e = cudaMemcpyFromSymbol(out4, g_wait_profile, sizeof(unsigned long long) * 4);
+    cudaError_t e = cudaMemcpyFromSymbol(out8, g_wait_profile, sizeof(unsigned long long) * 8);
     if (e != cudaSuccess) return cuda_fail(e);
-    unsigned long long zero[4] = { 0, 0, 0, 0 };
+    unsigned long long zero[8] = {};
     e = cudaMemcpyToSymbol(g_wait_profile, zero, sizeof(zero));
     return e == cudaSuccess ? NMSPMM_OK : cuda_fail(e);
 }

@@ -42,7 +42,7 @@ struct GemmArgs {
     const int* cinfo;
     float* C;
     float* partial;        // scratch slots of tile pieces, [slot][float4 e][thread]
-    unsigned* counters;    // one per tile, zero between calls
+    unsigned* counters;    // one per tile, zero between calls; nullptr: pieces stay in scratch for the reduction kernel
     int* status;           // device status word (0 = ok)
     int M, N, W;
     int tiles_x;           // tiles per row of tiles

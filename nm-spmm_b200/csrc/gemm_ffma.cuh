@@ -43,7 +43,7 @@ namespace nmspmm {
 // Diagnostic build (-DNMSPMM_PROFILE_WAITS): warp 0 of every CTA adds up the cycles
 // it spends waiting for a filled stage, filling a stage, and in total.
 #ifdef NMSPMM_PROFILE_WAITS
-extern __device__ unsigned long long g_wait_profile[4];
+extern __device__ unsigned long long g_wait_profile[8];
 #define NMSPMM_PROF_T(var) const long long var = clock64()
 #define NMSPMM_PROF_ADD(acc, t0) acc += clock64() - (t0)
 #else
@@ -161,7 +161,7 @@ nm_gemm_ffma_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
         if (j % NCW == warp) fill(j, u_begin + j);
 
 #ifdef NMSPMM_PROFILE_WAITS
-    long long prof_wait = 0, prof_fill = 0;
+    long long prof_wait = 0, prof_fill = 0, prof_epi = 0;
     const long long prof_start = clock64();
 #endif
     int s = 0, use = 0;                                    // stage of the window being multiplied, and its use count
@@ -325,6 +325,7 @@ nm_gemm_ffma_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
         }
 
         // ---------------------------------------------------------------- end of the piece
+        NMSPMM_PROF_T(te);
         const int ty = tile / g.tiles_x, tx = tile - ty * g.tiles_x;
         const int bj = tx * NS, bi = ty * MS;
         const int col0 = bj + vec * kVecLen + (lane >> 4) * 8 + (lane & 1) * 4;      // and col0 + 16
@@ -362,6 +363,10 @@ nm_gemm_ffma_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
                     __stcg(mine + (2 * i + 1) * NCT, make_float4(acc[i][2].x, acc[i][2].y, acc[i][3].x, acc[i][3].y));
                 }
             }
+            if (g.counters == nullptr) {                   // many pieces per tile: the reduction kernel adds them
+                cu += piece_n;
+                continue;
+            }
             __threadfence();
             __syncthreads();
             if (tid == 0) {
@@ -396,6 +401,7 @@ nm_gemm_ffma_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
             __syncthreads();                               // last_flag is reused by the next piece
         }
 
+        NMSPMM_PROF_ADD(prof_epi, te);
         cu += piece_n;                                     // on to the next piece of the range
     }
 #ifdef NMSPMM_PROFILE_WAITS
@@ -404,6 +410,9 @@ nm_gemm_ffma_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
         atomicAdd(&g_wait_profile[1], static_cast<unsigned long long>(prof_fill));
         atomicAdd(&g_wait_profile[2], static_cast<unsigned long long>(clock64() - prof_start));
         atomicAdd(&g_wait_profile[3], 1ull);
+        atomicAdd(&g_wait_profile[4], static_cast<unsigned long long>(prof_epi));
+        atomicMax(&g_wait_profile[5], static_cast<unsigned long long>(prof_epi));
+        atomicMax(&g_wait_profile[6], static_cast<unsigned long long>(clock64() - prof_start));
     }
 #endif
 }

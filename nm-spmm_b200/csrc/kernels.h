@@ -44,6 +44,10 @@ struct Tf32Variant {
 extern const Tf32Variant kTf32Variants[];
 extern const int kTf32VariantCount;
 
+// Adds the pieces the multiply left in scratch (args.counters == nullptr) for the tiles
+// first_tile .. first_tile + n_tiles - 1 of the given CTA tile and writes C.
+cudaError_t launch_reduce_pieces(int tile_id, const GemmArgs& args, int first_tile, int n_tiles, cudaStream_t st);
+
 // packed = 0: scalar FFMA loop; 1: two-lane packed FFMA2 loop.
 cudaError_t measure_ffma_peak(double* tflops, int packed, cudaStream_t st);
 
