@@ -96,7 +96,8 @@ int nmspmm_preprocess_high_host(int* column_info_host, int pruning_M, int prunin
 
 typedef struct nmspmm_gemm_desc {
     int M, N, K;
-    int n_keep;        /* kept rows per 32-window: 32, 16, 12 (LOW) / 8, 4 (HIGH); LOW also takes 8 */
+    int n_keep;        /* kept rows per 32-window: 32, 16, 12 (LOW) / 8, 4 (HIGH); LOW also takes 8.
+                          The TF32 path runs 12:32 as pairs of windows and wants K % 64 == 0 for it. */
     int format;        /* nmspmm_format */
     int layout_ns;     /* Ns the index buffers were packed for: 32, 64 or 128 */
     int path;          /* nmspmm_path */
@@ -111,9 +112,12 @@ typedef struct nmspmm_gemm_desc {
 size_t nmspmm_gemm_workspace_bytes(const nmspmm_gemm_desc* desc);
 
 /* Replaces the eight nmGEMM_*_matrices_{low,high}_sparsity launchers
- * (src/kernel_*.cu).  C is overwritten with A.B for every split_k (deterministic:
- * the pieces of a tile are summed in k order by the last one to arrive).  Asynchronous on
- * `stream`.  column_info_dev is NULL for NMSPMM_FORMAT_LOW. */
+ * (src/kernel_*.cu).  C is overwritten with A.B for every split_k.  The pieces of a tile
+ * are always summed in k order, so the result does not change from run to run: with up to
+ * four pieces per tile the last piece to arrive adds them inside the multiply; with more
+ * (deep K, few tiles) and for every split on the TF32 path the pieces stay in scratch and a
+ * second, small kernel adds them on the same stream.  Asynchronous on `stream`.
+ * column_info_dev is NULL for NMSPMM_FORMAT_LOW. */
 int nmspmm_gemm(const nmspmm_gemm_desc* desc,
                 const float* A_dev, const float* B_dev, const int* D_dev, const int* column_info_dev,
                 float* C_dev, void* workspace_dev, size_t workspace_bytes, void* stream);

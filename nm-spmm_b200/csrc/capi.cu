@@ -135,11 +135,11 @@ static int make_plan(const nmspmm_gemm_desc* d, int sms, Plan* p)
     if (rc != NMSPMM_OK) return rc;
     if (sms <= 0) sms = 148;
     if (d->path == NMSPMM_PATH_TF32) {
-        // Tensor-core path: one tile per CTA over all k windows (split_k is ignored).  Tile
-        // 128 x 256 with one CTA per SM is the faster one for the 64-k window formats once
-        // it fills the GPU (measured at 4096^3: 0.233 against 0.266 ms at 8:32, 0.166 against
-        // 0.232 ms at 4:32), tile 128 x 128 with two CTAs per SM for the 32-k window formats
-        // (0.360 against 0.424 ms at 16:32); the caller's tile wins over both.
+        // Tensor-core path: one CTA per tile and K slice.  Tile 128 x 256 with one CTA per
+        // SM is the faster one for the 64-k window formats once it fills the GPU (measured
+        // at 4096^3: 0.233 against 0.266 ms at 8:32, 0.166 against 0.232 ms at 4:32), tile
+        // 128 x 128 with two CTAs per SM for the 32-k window formats (0.360 against 0.424 ms
+        // at 16:32); the caller's tile wins over both.
         int want_ns = (mode == kModeHigh && ((d->N + 255) / 256) * ((d->M + 127) / 128) >= sms) ? 256 : 128;
         if (d->tile == kTile128x256) want_ns = 256;
         if (d->tile == kTile128x128) want_ns = 128;
@@ -154,10 +154,28 @@ static int make_plan(const nmspmm_gemm_desc* d, int sms, Plan* p)
         p->tiles_x = (d->N + p->tv->ns - 1) / p->tv->ns;
         p->tiles_y = (d->M + 127) / 128;
         const long long nt = static_cast<long long>(p->tiles_x) * p->tiles_y;
-        if (nt >= (1LL << 30)) return NMSPMM_UNSUPPORTED;
+        if (nt >= (1LL << 26)) return NMSPMM_UNSUPPORTED;
         p->n_tiles = static_cast<int>(nt);
-        p->split_k = 1;
-        p->n_dp = p->n_virtual = p->grid = p->n_tiles;
+        // K slices: the caller's number, or as many as fill the resident CTA slots with
+        // slices of at least four windows when the tiles alone do not.
+        const int resident = sms * (want_ns == 256 ? 1 : 2);
+        long long s = d->split_k;
+        if (s <= 0) {
+            s = resident / nt;
+            if (s > p->n_win / 4) s = p->n_win / 4;
+        }
+        if (s > p->n_win) s = p->n_win;
+        if (s < 1) s = 1;
+        if (nt * s >= (1LL << 30)) return NMSPMM_UNSUPPORTED;
+        p->split_k = static_cast<int>(s);
+        p->n_dp = (s == 1) ? p->n_tiles : 0;
+        p->n_virtual = p->grid = static_cast<int>(nt * s);
+        if (s > 1) {
+            p->slots = p->n_virtual;
+            p->deferred = true;
+            p->n_split_tiles = p->n_tiles;
+            p->partial_bytes = static_cast<size_t>(p->slots) * 128 * want_ns * sizeof(float);
+        }
         return NMSPMM_OK;
     }
     if (d->path != NMSPMM_PATH_FP32) return NMSPMM_UNSUPPORTED;
@@ -497,6 +515,7 @@ int nmspmm_gemm(const nmspmm_gemm_desc* desc, const float* A_dev, const float* B
                         : p.tv->launch(a, p.grid, static_cast<cudaStream_t>(stream));
     if (e == cudaSuccess && p.v && p.slots > 0 && p.deferred)
         e = launch_reduce_pieces(p.v->tile_id, a, p.first_split_tile, p.n_split_tiles, static_cast<cudaStream_t>(stream));
+    if (e == cudaSuccess && p.tv && p.split_k > 1) e = launch_reduce_slices(p.tv->ns, a, static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? NMSPMM_OK : cuda_fail(e);
 }
 

@@ -124,10 +124,14 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
     const uint32_t tmem_word = bar_acc + 8, abort_word = tmem_word + 4;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int tile = blockIdx.x;
+    // One CTA per (tile, K slice): with split_k slices per tile the accumulators go to
+    // the slice's scratch slot and the reduction kernel adds the slots.
+    const int n_slices = g.sched.split_k > 1 ? g.sched.split_k : 1;
+    const int tile = blockIdx.x / n_slices;
     const int ty = tile / g.tiles_x, tx = tile - ty * g.tiles_x;
     const int bi = ty * MS, bj = tx * NS;
-    const int n_win = g.sched.n_win;
+    int win0, n_win;                                       // this CTA's k windows: win0 .. win0 + n_win - 1
+    slice_range(g.sched.n_win, n_slices, blockIdx.x - tile * n_slices, win0, n_win);
     const int live_vecs = min(QT, (g.N - bj) / 32);        // vectors of the tile that exist
     const int qs_shift = g.qs_shift, layout_shift = qs_shift + 5;
     const int d_chunk = WS << qs_shift;
@@ -171,15 +175,15 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
                 mbar_arrive_expect_tx(full, Cfg::A_BYTES + live_vecs * (WS * 128) +
                                                 nlb * (d_bytes + (MODE == kModeHigh ? 256u : 0u)));
                 for (int b = 0; b < nlb; ++b) {            // the indices first: the gather starts from them
-                    const int* src = g.D + ((static_cast<size_t>(lb0 + b) * g.W) << qs_shift) + static_cast<size_t>(it) * d_chunk;
+                    const int* src = g.D + ((static_cast<size_t>(lb0 + b) * g.W) << qs_shift) + static_cast<size_t>(win0 + it) * d_chunk;
                     bulk_g2s(ds + b * d_bytes, src, d_bytes, full);
                     if (MODE == kModeHigh) {
-                        const int* ci = g.cinfo + (static_cast<size_t>(lb0 + b) * n_win + it) * 64;
+                        const int* ci = g.cinfo + (static_cast<size_t>(lb0 + b) * g.sched.n_win + win0 + it) * 64;
                         bulk_g2s(ds + Cfg::D_BYTES + b * 256, ci, 256, full);
                     }
                 }
-                tma_load_2d(as, &map_a, bi, it * KS, full);
-                for (int v = 0; v < live_vecs; ++v) tma_load_2d(st + v * (WS * 128), &map_b, bj + v * 32, it * WS, full);
+                tma_load_2d(as, &map_a, bi, (win0 + it) * KS, full);
+                for (int v = 0; v < live_vecs; ++v) tma_load_2d(st + v * (WS * 128), &map_b, bj + v * 32, (win0 + it) * WS, full);
             }
             __syncwarp();
         }
@@ -314,8 +318,10 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
                 uint32_t v[32];
                 tmem_ld_x32(tmem_addr(tmem, quad * 32, col), v);
                 tmem_wait_ld();
-                if (r < g.M) {
-                    float4* dst = reinterpret_cast<float4*>(g.C + static_cast<size_t>(r) * g.N + bj + col);
+                if (n_slices > 1 || r < g.M) {
+                    float4* dst = (n_slices > 1)
+                        ? reinterpret_cast<float4*>(g.partial + (static_cast<size_t>(blockIdx.x) * MS + row) * NS + col)
+                        : reinterpret_cast<float4*>(g.C + static_cast<size_t>(r) * g.N + bj + col);
 #pragma unroll
                     for (int x = 0; x < 8; ++x)
                         dst[x] = make_float4(__uint_as_float(v[4 * x]), __uint_as_float(v[4 * x + 1]),

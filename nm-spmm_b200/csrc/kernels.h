@@ -48,6 +48,10 @@ extern const int kTf32VariantCount;
 // first_tile .. first_tile + n_tiles - 1 of the given CTA tile and writes C.
 cudaError_t launch_reduce_pieces(int tile_id, const GemmArgs& args, int first_tile, int n_tiles, cudaStream_t st);
 
+// Adds the K slices the tensor-core multiply (tile 128 x ns, args.sched.split_k > 1)
+// left in scratch and writes C.
+cudaError_t launch_reduce_slices(int ns, const GemmArgs& args, cudaStream_t st);
+
 // packed = 0: scalar FFMA loop; 1: two-lane packed FFMA2 loop.
 cudaError_t measure_ffma_peak(double* tflops, int packed, cudaStream_t st);
 

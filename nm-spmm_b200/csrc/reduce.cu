@@ -94,4 +94,43 @@ cudaError_t launch_reduce_pieces(int tile_id, const GemmArgs& a, int first_tile,
     }
 }
 
+// The tensor-core path's K slices: slot (tile * split_k + z) holds the slice's 128 x NS
+// accumulator tile row-major.  One CTA adds the slices of 16 rows of a tile, in ascending
+// k order, and writes the rows and columns of C that exist.
+template <int NS>
+__global__ void __launch_bounds__(256) nm_reduce_slices_kernel(const GemmArgs g)
+{
+    constexpr int MS = 128, ROWS = 16, V4 = NS / 4;        // float4 words per tile row
+    const int tile = blockIdx.x / (MS / ROWS), r0 = (blockIdx.x % (MS / ROWS)) * ROWS;
+    const int ty = tile / g.tiles_x, tx = tile - ty * g.tiles_x;
+    const int bi = ty * MS, bj = tx * NS;
+    const int S = g.sched.split_k;
+    const float4* slots = reinterpret_cast<const float4*>(g.partial) + static_cast<size_t>(tile) * S * (MS * V4);
+    for (int e = threadIdx.x; e < ROWS * V4; e += 256) {
+        const int row = r0 + e / V4, c4 = e % V4;
+        if (bi + row >= g.M || bj + c4 * 4 >= g.N) continue;
+        const float4* src = slots + static_cast<size_t>(row) * V4 + c4;
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int z = 0; z < S; z += 4) {
+            float4 x[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (z + u < S) x[u] = __ldcg(src + static_cast<size_t>(z + u) * (MS * V4));
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (z + u < S) { sum.x += x[u].x; sum.y += x[u].y; sum.z += x[u].z; sum.w += x[u].w; }
+        }
+        *reinterpret_cast<float4*>(g.C + static_cast<size_t>(bi + row) * g.N + bj + c4 * 4) = sum;
+    }
+}
+
+cudaError_t launch_reduce_slices(int ns, const GemmArgs& a, cudaStream_t st)
+{
+    const int blocks = a.sched.n_tiles * (128 / 16);
+    if (ns == 256) nm_reduce_slices_kernel<256><<<blocks, 256, 0, st>>>(a);
+    else if (ns == 128) nm_reduce_slices_kernel<128><<<blocks, 256, 0, st>>>(a);
+    else return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
 }  // namespace nmspmm

@@ -62,6 +62,27 @@ def test_tf32_is_deterministic_and_close_to_the_exact_path(pkg):
     assert float((a - exact).norm() / exact.norm()) <= TF32_TOL
 
 
+@pytest.mark.parametrize("n_keep,tile,split_k", [(8, 1, 2), (8, 5, 3), (16, 1, 5), (12, 1, 2), (4, 5, 7), (8, 1, 64)])
+def test_tf32_k_slices(pkg, orc, n_keep, tile, split_k):
+    """K slices on the tensor-core path: each slice's accumulators go to scratch and the
+    reduction kernel adds them in k order (same result every run)."""
+    p = pkg.formats.make_random(200, 384, 1024, n_keep, seed=214)
+    want = orc.nm_gemm_f64(p.A_km, p.B_col, p.D_col)
+    op = pkg.NMSpMM.from_problem(p)
+    A = torch.from_numpy(p.A_km).cuda()
+    first = op.matmul(A, path=pkg.PATH_TF32, tile=tile, split_k=split_k)
+    assert rel_err(first.cpu().numpy(), want) <= TF32_TOL
+    assert torch.equal(op.matmul(A, path=pkg.PATH_TF32, tile=tile, split_k=split_k), first)
+    assert pkg.device_status() == 0
+
+
+def test_tf32_deep_k_automatic_slices(pkg, orc):
+    p = pkg.formats.make_random(128, 256, 16384, 4, seed=215)
+    info = pkg.plan(pkg.NMSpMM.from_problem(p).desc(p.M, path=pkg.PATH_TF32))
+    assert info.split_k > 1
+    assert rel_err(run(pkg, p), orc.nm_gemm_f64(p.A_km, p.B_col, p.D_col)) <= TF32_TOL
+
+
 def test_tf32_refuses_12_of_32_with_an_odd_number_of_windows(pkg):
     """12:32 runs as pairs of 32-k windows (24 kept rows = three K=8 instructions)."""
     p = pkg.formats.make_random(128, 256, 96, 12, seed=213)

@@ -111,13 +111,22 @@ def test_split_k_fills_the_machine_for_skinny_shapes(pkg):
     assert forced.split_k == 7 and forced.stream_k == 0 and forced.n_virtual == 8 * 7
     clamped = pkg.plan(pkg.make_desc(128, 128, 64, 16, 0, 128, split_k=9))
     assert clamped.split_k == 2            # only two windows exist
+    # the tensor-core path: slices when the tiles alone leave SMs idle, pieces always in scratch
+    tdeep = pkg.make_desc(128, 1024, 131072, 4, 1, 128, path=pkg.PATH_TF32)
+    info = pkg.plan(tdeep)
+    assert info.tile_n == 128 and info.split_k == 296 // 8 and info.grid == 8 * info.split_k
+    assert pkg.workspace_bytes(tdeep) == info.grid * 128 * 128 * 4
+    tbig = pkg.plan(pkg.make_desc(4096, 4096, 4096, 8, 1, 128, path=pkg.PATH_TF32))
+    assert tbig.tile_n == 256 and tbig.split_k == 1 and tbig.grid == 512
+    tlow = pkg.plan(pkg.make_desc(4096, 4096, 4096, 16, 0, 128, path=pkg.PATH_TF32))
+    assert tlow.tile_n == 128 and tlow.split_k == 1 and tlow.grid == 1024
     one = pkg.plan(pkg.make_desc(128, 128, 64, 16, 0, 128, split_k=1))
     assert one.split_k == 1 and pkg.workspace_bytes(pkg.make_desc(128, 128, 64, 16, 0, 128, split_k=1)) == 0
 
 
 @pytest.mark.parametrize("kw,status", [
     (dict(M=0), 1), (dict(N=100), 1), (dict(K=48), 1), (dict(M=6), 1), (dict(layout_ns=96), 1),
-    (dict(n_keep=10), 2), (dict(n_keep=16, fmt=1), 2), (dict(n_keep=4, fmt=0), 2), (dict(path=2), 2), (dict(path=1, n_keep=12), 2),
+    (dict(n_keep=10), 2), (dict(n_keep=16, fmt=1), 2), (dict(n_keep=4, fmt=0), 2), (dict(path=2), 2), (dict(path=1, n_keep=12, K=96), 2),
     (dict(N=192, layout_ns=128), 1), (dict(K=96, n_keep=8, fmt=1), 1), (dict(split_k=-1), 1),
 ])
 def test_bad_descriptions_are_rejected(pkg, kw, status):
