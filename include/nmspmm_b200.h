@@ -122,6 +122,22 @@ int nmspmm_gemm(const nmspmm_gemm_desc* desc,
                 const float* A_dev, const float* B_dev, const int* D_dev, const int* column_info_dev,
                 float* C_dev, void* workspace_dev, size_t workspace_bytes, void* stream);
 
+/* The multiply of one rank of a column-sharded B fused with the all-gather of C (no
+ * counterpart in the reference, which runs on one GPU).  The rank's problem is
+ * desc (N = the columns of its slab); every finished tile is stored, inside the multiply
+ * kernel, into n_out (1..8) row-major buffers of row stride ldc floats at column offset col0:
+ * the rank's own full-width C and the peer-mapped full-width C of every other rank (pointers
+ * that this process may store through: CUDA IPC, VMM or symmetric-memory mappings; plain
+ * st.global over NVLink, no multicast).  The stores ride along with the arithmetic instead
+ * of following it as a collective.  The call orders nothing between ranks: the caller makes
+ * sure every rank's C is free to be overwritten before the launch and that all ranks'
+ * launches have completed before any C is read (two barriers).  ldc >= col0 + N; ldc and
+ * col0 multiples of 4. */
+int nmspmm_gemm_gather(const nmspmm_gemm_desc* desc,
+                       const float* A_dev, const float* B_dev, const int* D_dev, const int* column_info_dev,
+                       float* const* C_all, int n_out, long long ldc, int col0,
+                       void* workspace_dev, size_t workspace_bytes, void* stream);
+
 /* Same, with scratch that the library allocates on first use and keeps per host thread
  * (cudaMalloc inside the first call that needs it).  For callers bound to the
  * reference's launcher signatures, which carry no workspace argument. */

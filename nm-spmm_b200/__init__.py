@@ -36,7 +36,7 @@ C_ABI_SYMBOLS = (
     "nmspmm_trans_index_host", "nmspmm_preprocess_low_host", "nmspmm_preprocess_high_host",
     "nmspmm_gemm_workspace_bytes", "nmspmm_gemm", "nmspmm_gemm_with_cached_workspace", "nmspmm_device_status",
     "nmspmm_gemm_plan", "nmspmm_gemm_host", "nmspmm_release_cached", "nmspmm_measure_ffma_peak",
-    "nmspmm_gemm_static_scratch",
+    "nmspmm_gemm_static_scratch", "nmspmm_gemm_gather",
 )
 STATIC_SCRATCH_BYTES = 16 << 20     # NMSPMM_STATIC_SCRATCH_BYTES of include/nmspmm_b200.h
 
@@ -89,6 +89,8 @@ def load_library():
     lib.nmspmm_gemm.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp, vp, sz, vp]
     lib.nmspmm_gemm_with_cached_workspace.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp, vp]
     lib.nmspmm_gemm_static_scratch.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp, vp]
+    lib.nmspmm_gemm_gather.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, ctypes.POINTER(vp), ci, ctypes.c_longlong, ci,
+                                       vp, sz, vp]
     lib.nmspmm_device_status.argtypes = [ctypes.POINTER(ci), ci]
     lib.nmspmm_gemm_plan.argtypes = [ctypes.POINTER(GemmDesc), ctypes.POINTER(PlanInfo)]
     lib.nmspmm_gemm_host.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp]
@@ -237,6 +239,22 @@ def gemm(desc: GemmDesc, A, B, D, column_info, C, workspace=None, stream=None) -
                                       ws_ptr, ws_bytes, _stream_ptr(stream)))
 
 
+def gemm_gather(desc: GemmDesc, A, B, D, column_info, out_ptrs, ldc: int, col0: int, workspace=None, stream=None) -> None:
+    """nmspmm_gemm_gather: the multiply of one rank's column slab, its finished tiles stored
+    into every buffer of ``out_ptrs`` (device addresses as ints: this rank's full-width C and
+    the peer-mapped full-width C of the other ranks) at column ``col0``, row stride ``ldc``."""
+    torch = _torch()
+    ws_ptr, ws_bytes = ctypes.c_void_p(0), 0
+    if workspace is not None:
+        ws_ptr, ws_bytes = ctypes.c_void_p(workspace.data_ptr()), workspace.numel() * workspace.element_size()
+    ci = ctypes.c_void_p(0) if column_info is None else _dev_ptr(column_info, torch.int32, "column_info")
+    ptrs = (ctypes.c_void_p * len(out_ptrs))(*[int(x) for x in out_ptrs])
+    _check("nmspmm_gemm_gather",
+           load_library().nmspmm_gemm_gather(ctypes.byref(desc), _dev_ptr(A, torch.float32, "A"), _dev_ptr(B, torch.float32, "B"),
+                                             _dev_ptr(D, torch.int32, "D"), ci, ptrs, len(out_ptrs), int(ldc), int(col0),
+                                             ws_ptr, ws_bytes, _stream_ptr(stream)))
+
+
 def gemm_static_scratch(desc: GemmDesc, A, B, D, column_info, C, stream=None) -> None:
     """nmspmm_gemm_static_scratch on CUDA tensors: the multiply with the library's built-in
     scratch array instead of a caller workspace, for callers that may not allocate.  Calls
@@ -361,3 +379,12 @@ class NMSpMM:
         C = torch.empty((M, self.N), dtype=torch.float32, device=A.device) if out is None else out
         gemm(d, A, self.B, self.D, self.column_info, C, self._scratch(workspace_bytes(d)))
         return C
+
+    def matmul_into(self, A, out_ptrs, ldc: int, col0: int, path: int = PATH_FP32, split_k: int = 0, tile: int = 0) -> None:
+        """The same multiply with its tiles stored into every buffer of ``out_ptrs`` (device
+        addresses) at column ``col0`` with row stride ``ldc``: the fused all-gather of a
+        column-sharded rank (see sharding.ShardedNMSpMM)."""
+        K, M = A.shape
+        assert K == self.K
+        d = self.desc(M, path, split_k, tile)
+        gemm_gather(d, A, self.B, self.D, self.column_info, out_ptrs, ldc, col0, self._scratch(workspace_bytes(d)))

@@ -476,8 +476,10 @@ int nmspmm_gemm_plan(const nmspmm_gemm_desc* desc, nmspmm_gemm_plan_info* out)
     return NMSPMM_OK;
 }
 
-int nmspmm_gemm(const nmspmm_gemm_desc* desc, const float* A_dev, const float* B_dev, const int* D_dev,
-                const int* column_info_dev, float* C_dev, void* workspace_dev, size_t workspace_bytes, void* stream)
+// The multiply with its outputs spelled out: n_out buffers, row stride ldc, first column col0.
+static int gemm_launch(const nmspmm_gemm_desc* desc, const float* A_dev, const float* B_dev, const int* D_dev,
+                       const int* column_info_dev, float* const* C_out, int n_out, long long ldc, int col0,
+                       void* workspace_dev, size_t workspace_bytes, void* stream)
 {
     DeviceInfo* di = nullptr;
     int rc = device_info(&di);
@@ -485,15 +487,23 @@ int nmspmm_gemm(const nmspmm_gemm_desc* desc, const float* A_dev, const float* B
     Plan p;
     rc = make_plan(desc, di->sms, &p);
     if (rc != NMSPMM_OK) return rc;
-    if (!A_dev || !B_dev || !D_dev || !C_dev) return NMSPMM_INVALID_ARGUMENT;
+    if (!A_dev || !B_dev || !D_dev || !C_out || n_out < 1 || n_out > kMaxOutputs) return NMSPMM_INVALID_ARGUMENT;
     if (desc->format == NMSPMM_FORMAT_HIGH && !column_info_dev) return NMSPMM_INVALID_ARGUMENT;
-    if (!aligned16(A_dev) || !aligned16(B_dev) || !aligned16(D_dev) || !aligned16(C_dev)) return NMSPMM_INVALID_ARGUMENT;
+    if (!aligned16(A_dev) || !aligned16(B_dev) || !aligned16(D_dev)) return NMSPMM_INVALID_ARGUMENT;
+    if (ldc < static_cast<long long>(col0) + desc->N || col0 < 0 || ldc % 4 != 0 || col0 % 4 != 0) return NMSPMM_INVALID_ARGUMENT;
     GemmArgs a {};
     a.A = A_dev;
     a.B = B_dev;
     a.D = D_dev;
     a.cinfo = column_info_dev;
-    a.C = C_dev;
+    GemmOutputs outs {};
+    for (int o = 0; o < n_out; ++o) {
+        if (!C_out[o] || !aligned16(C_out[o])) return NMSPMM_INVALID_ARGUMENT;
+        if (o == 0) a.C = C_out[o]; else outs.C_more[o - 1] = C_out[o];
+    }
+    outs.n_out = n_out;
+    outs.ldc = ldc;
+    outs.col0 = col0;
     a.status = di->status_word;
     a.M = desc->M;
     a.N = desc->N;
@@ -511,12 +521,28 @@ int nmspmm_gemm(const nmspmm_gemm_desc* desc, const float* A_dev, const float* B
         a.counters = p.deferred ? nullptr : static_cast<unsigned*>(workspace_dev);
         a.partial = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace_dev) + p.counters_bytes);
     }
-    cudaError_t e = p.v ? p.v->launch(a, p.grid, static_cast<cudaStream_t>(stream))
-                        : p.tv->launch(a, p.grid, static_cast<cudaStream_t>(stream));
+    const bool plain = (n_out == 1 && ldc == desc->N && col0 == 0);
+    cudaError_t e = p.v ? (plain ? p.v->launch : p.v->launch_multi)(a, outs, p.grid, static_cast<cudaStream_t>(stream))
+                        : p.tv->launch(a, outs, p.grid, static_cast<cudaStream_t>(stream));
     if (e == cudaSuccess && p.v && p.slots > 0 && p.deferred)
-        e = launch_reduce_pieces(p.v->tile_id, a, p.first_split_tile, p.n_split_tiles, static_cast<cudaStream_t>(stream));
-    if (e == cudaSuccess && p.tv && p.split_k > 1) e = launch_reduce_slices(p.tv->ns, a, static_cast<cudaStream_t>(stream));
+        e = launch_reduce_pieces(p.v->tile_id, a, outs, p.first_split_tile, p.n_split_tiles, static_cast<cudaStream_t>(stream));
+    if (e == cudaSuccess && p.tv && p.split_k > 1) e = launch_reduce_slices(p.tv->ns, a, outs, static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? NMSPMM_OK : cuda_fail(e);
+}
+
+int nmspmm_gemm(const nmspmm_gemm_desc* desc, const float* A_dev, const float* B_dev, const int* D_dev,
+                const int* column_info_dev, float* C_dev, void* workspace_dev, size_t workspace_bytes, void* stream)
+{
+    if (!desc) return NMSPMM_INVALID_ARGUMENT;
+    float* out[1] = { C_dev };
+    return gemm_launch(desc, A_dev, B_dev, D_dev, column_info_dev, out, 1, desc->N, 0, workspace_dev, workspace_bytes, stream);
+}
+
+int nmspmm_gemm_gather(const nmspmm_gemm_desc* desc, const float* A_dev, const float* B_dev, const int* D_dev,
+                       const int* column_info_dev, float* const* C_all, int n_out, long long ldc, int col0,
+                       void* workspace_dev, size_t workspace_bytes, void* stream)
+{
+    return gemm_launch(desc, A_dev, B_dev, D_dev, column_info_dev, C_all, n_out, ldc, col0, workspace_dev, workspace_bytes, stream);
 }
 
 int nmspmm_device_status(int* status_out, int clear)

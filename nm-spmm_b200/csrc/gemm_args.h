@@ -35,6 +35,8 @@ struct UnitSchedule {
     int n_tiles, n_win, n_virtual, split_k, n_dp;
 };
 
+constexpr int kMaxOutputs = 8;    // copies of C a launch can write (one per GPU of a box)
+
 struct GemmArgs {
     const float* A;
     const float* B;
@@ -49,6 +51,20 @@ struct GemmArgs {
     UnitSchedule sched;    // n_tiles, n_win (k windows per tile, W / WS), ranges
     int qs_shift;          // log2 of the vectors per packed index block (layout_ns / 32): 0, 1 or 2
 };
+
+// Where finished tiles go when there is more than the private M x N matrix C: n_out row-major
+// buffers (args.C, then C_more[0 .. n_out-2]) with row stride ldc, this problem's columns
+// starting at column col0 of each.  A column-sharded rank that also gathers passes its own
+// full-width C and every peer's (peer-mapped pointers; plain stores over NVLink).  A
+// separate block, handed only to the kernels compiled for it: the plain kernels' register
+// allocation is sensitive even to the size of their argument block.
+struct GemmOutputs {
+    float* C_more[kMaxOutputs - 1];
+    int n_out;
+    int col0;
+    long long ldc;
+};
+NMSPMM_HD float* output_of(const GemmArgs& a, const GemmOutputs& o, int i) { return i == 0 ? a.C : o.C_more[i - 1]; }
 
 // Which windows (of n_win) slice z of split_k owns: the first n_win % split_k
 // slices get one extra window (the split of src/kernel_64x128_8x8.cu:21-37 of the

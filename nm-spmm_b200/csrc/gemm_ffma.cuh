@@ -81,9 +81,13 @@ struct FfmaCfg {
     static_assert(THREADS <= 512, "tile too large");
 };
 
-template <int MS, int NS, int WM, int WS, int KS_, int MODE>
-__global__ void __launch_bounds__((FfmaCfg<MS, NS, WM, WS, KS_, MODE>::THREADS), (FfmaCfg<MS, NS, WM, WS, KS_, MODE>::MIN_BLOCKS))
-nm_gemm_ffma_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b)
+// MULTI: finished tiles go to every buffer of g.C at (ldc, col0) -- the fused all-gather of a
+// column-sharded rank; otherwise to g.C[0] as a private M x N matrix.  A template flag, not a
+// run-time one: the kernel sits at the edge of its 128-register budget and the extra
+// loop in the epilogue cost the plain form 5-10 % through the register allocation alone.
+template <int MS, int NS, int WM, int WS, int KS_, int MODE, bool MULTI>
+__device__ __forceinline__ void nm_gemm_ffma_body(const GemmArgs& g, const CUtensorMap& map_a, const CUtensorMap& map_b,
+                                                  const GemmOutputs& outs)
 {
     using Cfg = FfmaCfg<MS, NS, WM, WS, KS_, MODE>;
     constexpr int KS = Cfg::KS, QT = Cfg::QT, NCW = Cfg::NCW, NCT = Cfg::NCT, MT = Cfg::MT, STAGES = Cfg::STAGES;
@@ -339,9 +343,18 @@ nm_gemm_ffma_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
             for (int i = 0; i < MT; ++i) {
                 const int r = row_of(i);
                 if (r < g.M) {
-                    float* cp = g.C + static_cast<size_t>(r) * g.N + col0;
-                    *reinterpret_cast<float4*>(cp) = make_float4(acc[i][0].x, acc[i][0].y, acc[i][1].x, acc[i][1].y);
-                    *reinterpret_cast<float4*>(cp + 16) = make_float4(acc[i][2].x, acc[i][2].y, acc[i][3].x, acc[i][3].y);
+                    if constexpr (MULTI) {
+                        const size_t at = static_cast<size_t>(r) * outs.ldc + outs.col0 + col0;
+                        for (int o = 0; o < outs.n_out; ++o) {   // every output (peers' copies of C when gathering)
+                            float* cp = output_of(g, outs, o) + at;
+                            *reinterpret_cast<float4*>(cp) = make_float4(acc[i][0].x, acc[i][0].y, acc[i][1].x, acc[i][1].y);
+                            *reinterpret_cast<float4*>(cp + 16) = make_float4(acc[i][2].x, acc[i][2].y, acc[i][3].x, acc[i][3].y);
+                        }
+                    } else {
+                        float* cp = g.C + static_cast<size_t>(r) * g.N + col0;
+                        *reinterpret_cast<float4*>(cp) = make_float4(acc[i][0].x, acc[i][0].y, acc[i][1].x, acc[i][1].y);
+                        *reinterpret_cast<float4*>(cp + 16) = make_float4(acc[i][2].x, acc[i][2].y, acc[i][3].x, acc[i][3].y);
+                    }
                 }
             }
         };
@@ -417,20 +430,40 @@ nm_gemm_ffma_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
 #endif
 }
 
+// The two kernels: private C (the argument block of old), and C to several buffers.
+template <int MS, int NS, int WM, int WS, int KS_, int MODE>
+__global__ void __launch_bounds__((FfmaCfg<MS, NS, WM, WS, KS_, MODE>::THREADS), (FfmaCfg<MS, NS, WM, WS, KS_, MODE>::MIN_BLOCKS))
+nm_gemm_ffma_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b)
+{
+    nm_gemm_ffma_body<MS, NS, WM, WS, KS_, MODE, false>(g, map_a, map_b, GemmOutputs {});
+}
+
+template <int MS, int NS, int WM, int WS, int KS_, int MODE>
+__global__ void __launch_bounds__((FfmaCfg<MS, NS, WM, WS, KS_, MODE>::THREADS), (FfmaCfg<MS, NS, WM, WS, KS_, MODE>::MIN_BLOCKS))
+nm_gemm_ffma_multi_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                          const GemmOutputs outs)
+{
+    nm_gemm_ffma_body<MS, NS, WM, WS, KS_, MODE, true>(g, map_a, map_b, outs);
+}
+
 // Host-side launcher of one variant: encodes the two tensor maps (A as [K][M] with an
 // MS x KS box, B as [W][N] with an NS x WS box) and sets the dynamic shared-memory
 // limit once per device.
-template <int MS, int NS, int WM, int WS, int KS_, int MODE>
-cudaError_t launch_ffma(const GemmArgs& a, int grid, cudaStream_t st)
+template <int MS, int NS, int WM, int WS, int KS_, int MODE, bool MULTI>
+cudaError_t launch_ffma(const GemmArgs& a, const GemmOutputs& outs, int grid, cudaStream_t st)
 {
     using Cfg = FfmaCfg<MS, NS, WM, WS, KS_, MODE>;
-    auto kernel = nm_gemm_ffma_kernel<MS, NS, WM, WS, KS_, MODE>;
     static bool configured[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 64 && !configured[dev]) {
-        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+        if (MULTI)
+            e = cudaFuncSetAttribute(nm_gemm_ffma_multi_kernel<MS, NS, WM, WS, KS_, MODE>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+        else
+            e = cudaFuncSetAttribute(nm_gemm_ffma_kernel<MS, NS, WM, WS, KS_, MODE>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
@@ -439,14 +472,18 @@ cudaError_t launch_ffma(const GemmArgs& a, int grid, cudaStream_t st)
     if (e != cudaSuccess) return e;
     e = encode_tensor_map_2d(&map_b, a.B, a.N, a.W, NS, WS);
     if (e != cudaSuccess) return e;
-    kernel<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(a, map_a, map_b);
+    if (MULTI)
+        nm_gemm_ffma_multi_kernel<MS, NS, WM, WS, KS_, MODE><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(a, map_a, map_b, outs);
+    else
+        nm_gemm_ffma_kernel<MS, NS, WM, WS, KS_, MODE><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(a, map_a, map_b);
     return cudaGetLastError();
 }
 
 #define NMSPMM_FFMA_VARIANT(ID, NKEEP, MS, NS, WM, WS, KS, MODE)                                            \
     FfmaVariant { ID, MS, NS, NKEEP, WS, KS, MODE, FfmaCfg<MS, NS, WM, WS, KS, MODE>::THREADS,               \
                   FfmaCfg<MS, NS, WM, WS, KS, MODE>::SMEM_BYTES, FfmaCfg<MS, NS, WM, WS, KS, MODE>::STAGES,  \
-                  FfmaCfg<MS, NS, WM, WS, KS, MODE>::MIN_BLOCKS, &launch_ffma<MS, NS, WM, WS, KS, MODE> }
+                  FfmaCfg<MS, NS, WM, WS, KS, MODE>::MIN_BLOCKS, &launch_ffma<MS, NS, WM, WS, KS, MODE, false>,     \
+                  &launch_ffma<MS, NS, WM, WS, KS, MODE, true> }
 
 // All tiles for one (kept rows per 32-window, B rows per stage, A rows per stage, MODE).
 #define NMSPMM_FFMA_TILES(NKEEP, WS, KS, MODE)                            \

@@ -109,7 +109,8 @@ __device__ __forceinline__ void tmem_st_chunk(uint32_t taddr, const uint32_t (&v
 
 template <int WS, int KS_, int MODE, int QT_>
 __global__ void __launch_bounds__((Tf32Cfg<WS, KS_, MODE, QT_>::THREADS), (Tf32Cfg<WS, KS_, MODE, QT_>::CTAS_PER_SM))
-nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b)
+nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const GemmOutputs outs)
 {
     using Cfg = Tf32Cfg<WS, KS_, MODE, QT_>;
     constexpr int MS = Cfg::MS, NS = Cfg::NS, QT = Cfg::QT, KS = Cfg::KS, G = Cfg::G, STAGES = Cfg::STAGES, NBUF = Cfg::NBUF;
@@ -318,14 +319,21 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
                 uint32_t v[32];
                 tmem_ld_x32(tmem_addr(tmem, quad * 32, col), v);
                 tmem_wait_ld();
-                if (n_slices > 1 || r < g.M) {
-                    float4* dst = (n_slices > 1)
-                        ? reinterpret_cast<float4*>(g.partial + (static_cast<size_t>(blockIdx.x) * MS + row) * NS + col)
-                        : reinterpret_cast<float4*>(g.C + static_cast<size_t>(r) * g.N + bj + col);
+                if (n_slices > 1) {
+                    float4* dst = reinterpret_cast<float4*>(g.partial + (static_cast<size_t>(blockIdx.x) * MS + row) * NS + col);
 #pragma unroll
                     for (int x = 0; x < 8; ++x)
                         dst[x] = make_float4(__uint_as_float(v[4 * x]), __uint_as_float(v[4 * x + 1]),
                                              __uint_as_float(v[4 * x + 2]), __uint_as_float(v[4 * x + 3]));
+                } else if (r < g.M) {
+                    const size_t at = static_cast<size_t>(r) * outs.ldc + outs.col0 + bj + col;
+                    for (int o = 0; o < outs.n_out; ++o) {   // every output (peers' copies of C when gathering)
+                        float4* dst = reinterpret_cast<float4*>(output_of(g, outs, o) + at);
+#pragma unroll
+                        for (int x = 0; x < 8; ++x)
+                            dst[x] = make_float4(__uint_as_float(v[4 * x]), __uint_as_float(v[4 * x + 1]),
+                                                 __uint_as_float(v[4 * x + 2]), __uint_as_float(v[4 * x + 3]));
+                    }
                 }
             }
         } else if (lane == 0) {
@@ -341,7 +349,7 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
 }
 
 template <int WS, int KS, int MODE, int QT>
-static cudaError_t launch_tf32(const GemmArgs& a, int tiles, cudaStream_t st)
+static cudaError_t launch_tf32(const GemmArgs& a, const GemmOutputs& outs, int tiles, cudaStream_t st)
 {
     using Cfg = Tf32Cfg<WS, KS, MODE, QT>;
     auto kernel = nm_gemm_tf32_kernel<WS, KS, MODE, QT>;
@@ -359,7 +367,7 @@ static cudaError_t launch_tf32(const GemmArgs& a, int tiles, cudaStream_t st)
     if (e != cudaSuccess) return e;
     e = encode_tensor_map_2d(&map_b, a.B, a.N, a.W, 32, WS, 1);      // 32-byte chunks swizzled in 128-byte rows
     if (e != cudaSuccess) return e;
-    kernel<<<tiles, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(a, map_a, map_b);
+    kernel<<<tiles, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(a, map_a, map_b, outs);
     return cudaGetLastError();
 }
 

@@ -20,7 +20,8 @@ struct FfmaVariant {
     int ks;             // rows of A per staged window (32, or 64: a merged HIGH window)
     int mode;           // kModeLow / kModeHigh
     int threads, smem_bytes, stages, min_blocks;
-    cudaError_t (*launch)(const GemmArgs&, int grid, cudaStream_t st);
+    cudaError_t (*launch)(const GemmArgs&, const GemmOutputs&, int grid, cudaStream_t st);         // private M x N matrix args.C
+    cudaError_t (*launch_multi)(const GemmArgs&, const GemmOutputs&, int grid, cudaStream_t st);   // every output at (ldc, col0)
 };
 // Returns nullptr when the combination was not compiled.
 const FfmaVariant* find_ffma_variant(int tile_id, int n_keep, int mode);
@@ -39,18 +40,19 @@ struct Tf32Variant {
     int mode;
     int ns;             // tile columns: 256 (one CTA per SM) or 128 (two)
     int smem_bytes, stages;
-    cudaError_t (*launch)(const GemmArgs&, int tiles, cudaStream_t st);
+    cudaError_t (*launch)(const GemmArgs&, const GemmOutputs&, int tiles, cudaStream_t st);
 };
 extern const Tf32Variant kTf32Variants[];
 extern const int kTf32VariantCount;
 
 // Adds the pieces the multiply left in scratch (args.counters == nullptr) for the tiles
 // first_tile .. first_tile + n_tiles - 1 of the given CTA tile and writes C.
-cudaError_t launch_reduce_pieces(int tile_id, const GemmArgs& args, int first_tile, int n_tiles, cudaStream_t st);
+cudaError_t launch_reduce_pieces(int tile_id, const GemmArgs& args, const GemmOutputs& outs, int first_tile, int n_tiles,
+                                 cudaStream_t st);
 
 // Adds the K slices the tensor-core multiply (tile 128 x ns, args.sched.split_k > 1)
 // left in scratch and writes C.
-cudaError_t launch_reduce_slices(int ns, const GemmArgs& args, cudaStream_t st);
+cudaError_t launch_reduce_slices(int ns, const GemmArgs& args, const GemmOutputs& outs, cudaStream_t st);
 
 // packed = 0: scalar FFMA loop; 1: two-lane packed FFMA2 loop.
 cudaError_t measure_ffma_peak(double* tflops, int packed, cudaStream_t st);

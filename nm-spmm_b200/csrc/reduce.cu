@@ -34,7 +34,7 @@ struct FragmentMap {
 
 template <int MS, int NS, int WM>
 __global__ void __launch_bounds__((FragmentMap<MS, NS, WM>::NCT))
-nm_reduce_pieces_kernel(const GemmArgs g, int first_tile)
+nm_reduce_pieces_kernel(const GemmArgs g, const GemmOutputs outs, int first_tile)
 {
     using Map = FragmentMap<MS, NS, WM>;
     constexpr int NCT = Map::NCT, MT = Map::MT;
@@ -68,28 +68,31 @@ nm_reduce_pieces_kernel(const GemmArgs g, int first_tile)
             }
         }
     }
-    float* cp = g.C + static_cast<size_t>(r) * g.N + c;
-    *reinterpret_cast<float4*>(cp) = sx;
-    *reinterpret_cast<float4*>(cp + 16) = sy;
+    const size_t at = static_cast<size_t>(r) * outs.ldc + outs.col0 + c;
+    for (int o = 0; o < outs.n_out; ++o) {
+        float* cp = output_of(g, outs, o) + at;
+        *reinterpret_cast<float4*>(cp) = sx;
+        *reinterpret_cast<float4*>(cp + 16) = sy;
+    }
 }
 
 template <int MS, int NS, int WM>
-static cudaError_t launch_reduce(const GemmArgs& a, int first_tile, int n_tiles, cudaStream_t st)
+static cudaError_t launch_reduce(const GemmArgs& a, const GemmOutputs& outs, int first_tile, int n_tiles, cudaStream_t st)
 {
     using Map = FragmentMap<MS, NS, WM>;
-    nm_reduce_pieces_kernel<MS, NS, WM><<<n_tiles * Map::MT, Map::NCT, 0, st>>>(a, first_tile);
+    nm_reduce_pieces_kernel<MS, NS, WM><<<n_tiles * Map::MT, Map::NCT, 0, st>>>(a, outs, first_tile);
     return cudaGetLastError();
 }
 
-cudaError_t launch_reduce_pieces(int tile_id, const GemmArgs& a, int first_tile, int n_tiles, cudaStream_t st)
+cudaError_t launch_reduce_pieces(int tile_id, const GemmArgs& a, const GemmOutputs& outs, int first_tile, int n_tiles, cudaStream_t st)
 {
     if (n_tiles <= 0) return cudaSuccess;
     switch (tile_id) {
-    case kTile128x128: return launch_reduce<128, 128, 64>(a, first_tile, n_tiles, st);
-    case kTile64x128: return launch_reduce<64, 128, 64>(a, first_tile, n_tiles, st);
-    case kTile32x128: return launch_reduce<32, 128, 32>(a, first_tile, n_tiles, st);
-    case kTile16x128: return launch_reduce<16, 128, 16>(a, first_tile, n_tiles, st);
-    case kTile128x256: return launch_reduce<128, 256, 64>(a, first_tile, n_tiles, st);
+    case kTile128x128: return launch_reduce<128, 128, 64>(a, outs, first_tile, n_tiles, st);
+    case kTile64x128: return launch_reduce<64, 128, 64>(a, outs, first_tile, n_tiles, st);
+    case kTile32x128: return launch_reduce<32, 128, 32>(a, outs, first_tile, n_tiles, st);
+    case kTile16x128: return launch_reduce<16, 128, 16>(a, outs, first_tile, n_tiles, st);
+    case kTile128x256: return launch_reduce<128, 256, 64>(a, outs, first_tile, n_tiles, st);
     default: return cudaErrorInvalidValue;
     }
 }
@@ -98,7 +101,7 @@ cudaError_t launch_reduce_pieces(int tile_id, const GemmArgs& a, int first_tile,
 // accumulator tile row-major.  One CTA adds the slices of 16 rows of a tile, in ascending
 // k order, and writes the rows and columns of C that exist.
 template <int NS>
-__global__ void __launch_bounds__(256) nm_reduce_slices_kernel(const GemmArgs g)
+__global__ void __launch_bounds__(256) nm_reduce_slices_kernel(const GemmArgs g, const GemmOutputs outs)
 {
     constexpr int MS = 128, ROWS = 16, V4 = NS / 4;        // float4 words per tile row
     const int tile = blockIdx.x / (MS / ROWS), r0 = (blockIdx.x % (MS / ROWS)) * ROWS;
@@ -120,15 +123,16 @@ __global__ void __launch_bounds__(256) nm_reduce_slices_kernel(const GemmArgs g)
             for (int u = 0; u < 4; ++u)
                 if (z + u < S) { sum.x += x[u].x; sum.y += x[u].y; sum.z += x[u].z; sum.w += x[u].w; }
         }
-        *reinterpret_cast<float4*>(g.C + static_cast<size_t>(bi + row) * g.N + bj + c4 * 4) = sum;
+        const size_t at = static_cast<size_t>(bi + row) * outs.ldc + outs.col0 + bj + c4 * 4;
+        for (int o = 0; o < outs.n_out; ++o) *reinterpret_cast<float4*>(output_of(g, outs, o) + at) = sum;
     }
 }
 
-cudaError_t launch_reduce_slices(int ns, const GemmArgs& a, cudaStream_t st)
+cudaError_t launch_reduce_slices(int ns, const GemmArgs& a, const GemmOutputs& outs, cudaStream_t st)
 {
     const int blocks = a.sched.n_tiles * (128 / 16);
-    if (ns == 256) nm_reduce_slices_kernel<256><<<blocks, 256, 0, st>>>(a);
-    else if (ns == 128) nm_reduce_slices_kernel<128><<<blocks, 256, 0, st>>>(a);
+    if (ns == 256) nm_reduce_slices_kernel<256><<<blocks, 256, 0, st>>>(a, outs);
+    else if (ns == 128) nm_reduce_slices_kernel<128><<<blocks, 256, 0, st>>>(a, outs);
     else return cudaErrorInvalidValue;
     return cudaGetLastError();
 }

@@ -67,8 +67,49 @@ class ShardedNMSpMM:
         self.N, self.world, self.rank, self.layout_ns = BT.shape[1], world, rank, layout_ns
         bt, dt, self.columns = shard_operands(BT, DT, rank, world, layout_ns)
         self.local = pkg.NMSpMM(bt, dt, K, n_keep, layout_ns, device=device)
+        self._symm = None
 
-    def matmul(self, A, gather: bool = False, **kw):
-        """Local slab C[:, c0:c1]; with ``gather`` the full C on every rank."""
+    def matmul(self, A, gather=False, **kw):
+        """Local slab C[:, c0:c1]; with ``gather`` the full C on every rank.
+
+        ``gather=True`` runs the multiply and then an NCCL all-gather of the slabs.
+        ``gather="fused"`` lets the multiply kernel itself store every finished tile into the
+        full-width C of all ranks (peer-mapped symmetric memory, plain stores over NVLink),
+        so the transfer overlaps the arithmetic; the returned tensor is this rank's
+        symmetric buffer, valid until the next fused call with the same row count."""
+        if gather == "fused":
+            return self._matmul_fused(A, **kw)
         C_local = self.local.matmul(A, **kw)
         return all_gather_columns(C_local, self.N, self.world, self.layout_ns) if gather else C_local
+
+    def _symmetric_c(self, M: int, device):
+        """Full-width C in symmetric memory and every rank's mapping of it (made once per M)."""
+        import os
+
+        import torch
+        import torch.distributed as dist
+        # plain peer mappings are all this path uses: no NVLink multicast object is bound
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+
+        if self._symm is None or self._symm[0] != M:
+            buf = symm_mem.empty((M, self.N), dtype=torch.float32, device=device)
+            hdl = symm_mem.rendezvous(buf, dist.group.WORLD)
+            ptrs = [int(p) for p in hdl.buffer_ptrs]
+            # this rank's buffer first, then the peers in ring order (spreads the NVLink
+            # traffic: at any moment different ranks write to different peers)
+            order = [(self.rank + i) % self.world for i in range(self.world)]
+            self._symm = (M, buf, hdl, [ptrs[r] for r in order], torch.zeros(1, device=device))
+        return self._symm
+
+    def _matmul_fused(self, A, **kw):
+        import torch.distributed as dist
+
+        _, buf, _, ptrs, flag = self._symmetric_c(A.shape[1], A.device)
+        # Two stream-ordered barriers (a one-element NCCL all-reduce each): before the launch
+        # every rank has finished reading the previous result out of its buffer; after it
+        # every rank's stores have landed everywhere.
+        dist.all_reduce(flag)
+        self.local.matmul_into(A, ptrs, self.N, self.columns[0], **kw)
+        dist.all_reduce(flag)
+        return buf

@@ -1,4 +1,5 @@
-"""Column-sharded multiply on two GPUs with the optional all-gather of C over NCCL.
+"""Column-sharded multiply on two GPUs with the optional all-gather of C: over NCCL after
+the multiply, and fused into the multiply (stores into the peers' symmetric buffers).
 Skipped on a single-GPU machine (the CPU ranks of test_sharding_gloo.py cover the
 partition logic there).  NVLS is left off: the ranks are short-lived test processes."""
 import os
@@ -41,11 +42,16 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
             A = torch.from_numpy(p.A_km).cuda()
             C = op.matmul(A, gather=True, path=path)
             torch.cuda.synchronize()
-            if rank == 0:
-                orc = oracle.restatement()
-                want = orc.nm_gemm_f32(p.A_km, p.B_col, p.D_col).astype(np.float64)
-                err = np.linalg.norm(C.cpu().numpy() - want) / np.linalg.norm(want)
-                ok = ok and C.shape == (M, N) and err <= tol
+            orc = oracle.restatement()
+            want = orc.nm_gemm_f32(p.A_km, p.B_col, p.D_col).astype(np.float64)
+            err = np.linalg.norm(C.cpu().numpy() - want) / np.linalg.norm(want)
+            ok = ok and C.shape == (M, N) and err <= tol
+            # the gather fused into the multiply: peers' tiles arrive by their kernels' stores
+            for split_k in (0, 3, 8):                      # whole tiles, in-kernel reduction, reduction kernel
+                F = op.matmul(A, gather="fused", path=path, split_k=split_k)
+                torch.cuda.synchronize()
+                same = torch.equal(F, C) if split_k == 0 else float((F - C).norm() / C.norm()) <= 1e-6
+                ok = ok and F.shape == (M, N) and same
             ok = ok and pkg.device_status() == 0
         open(os.path.join(out_dir, f"rank{rank}.ok"), "w").write("1" if ok else "0")
     finally:
