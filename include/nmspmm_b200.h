@@ -84,6 +84,17 @@ int nmspmm_preprocess_high_device(const int* DT_dev, int* D_dev, int* column_inf
                                   int pruning_M, int pruning_N, int W, int Q, int Ns,
                                   int fuse_trans_index, int column_info_tail_ints, void* stream);
 
+/* Vector-wise N:M magnitude pruning of a dense weight on the GPU (no counterpart in the
+ * reference, whose test driver draws random indices on the host, include/utils.h:46-64; this
+ * produces the same formats from real weights without a round trip through the host).
+ * dense_dev is row-major [K][N].  In every 32-row window and for every vector of vec_len (32
+ * or 64) columns the n_keep rows with the largest sum of squares over the vector's columns are
+ * kept (ties to the lower row), in ascending order: BT_dev [K/32*n_keep][N] receives their
+ * values, DT_dev [K/32*n_keep][N/32] their window-local indices (one per 32 columns; with
+ * vec_len 64 adjacent pairs are equal) -- the inputs of nmspmm_preprocess_*_device. */
+int nmspmm_prune_device(const float* dense_dev, float* BT_dev, int* DT_dev,
+                        int K, int N, int n_keep, int vec_len, void* stream);
+
 /* Host-pointer forms with the reference's in-place semantics (H2D + kernel + D2H;
  * they allocate and free temporary device buffers).  The extra column_info window
  * is left untouched, like the reference. */

@@ -18,7 +18,7 @@ from typing import Optional
 
 import numpy as np
 
-from . import build, formats, sharding  # noqa: F401  (in-tree nvcc build; seeded operands; multi-GPU partition)
+from . import build, formats, linear, sharding  # noqa: F401  (in-tree nvcc build; seeded operands; layer; multi-GPU partition)
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 # NMSPMM_LIBRARY selects another build of the same library (A/B comparisons of kernels).
@@ -36,7 +36,7 @@ C_ABI_SYMBOLS = (
     "nmspmm_trans_index_host", "nmspmm_preprocess_low_host", "nmspmm_preprocess_high_host",
     "nmspmm_gemm_workspace_bytes", "nmspmm_gemm", "nmspmm_gemm_with_cached_workspace", "nmspmm_device_status",
     "nmspmm_gemm_plan", "nmspmm_gemm_host", "nmspmm_release_cached", "nmspmm_measure_ffma_peak",
-    "nmspmm_gemm_static_scratch", "nmspmm_gemm_gather",
+    "nmspmm_gemm_static_scratch", "nmspmm_gemm_gather", "nmspmm_prune_device",
 )
 STATIC_SCRATCH_BYTES = 16 << 20     # NMSPMM_STATIC_SCRATCH_BYTES of include/nmspmm_b200.h
 
@@ -89,6 +89,7 @@ def load_library():
     lib.nmspmm_gemm.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp, vp, sz, vp]
     lib.nmspmm_gemm_with_cached_workspace.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp, vp]
     lib.nmspmm_gemm_static_scratch.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp, vp]
+    lib.nmspmm_prune_device.argtypes = [vp, vp, vp, ci, ci, ci, ci, vp]
     lib.nmspmm_gemm_gather.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, ctypes.POINTER(vp), ci, ctypes.c_longlong, ci,
                                        vp, sz, vp]
     lib.nmspmm_device_status.argtypes = [ctypes.POINTER(ci), ci]
@@ -239,6 +240,20 @@ def gemm(desc: GemmDesc, A, B, D, column_info, C, workspace=None, stream=None) -
                                       ws_ptr, ws_bytes, _stream_ptr(stream)))
 
 
+def prune_device(dense, n_keep: int, vec_len: int = 32, stream=None):
+    """nmspmm_prune_device: vector-wise ``n_keep``:32 magnitude pruning of a dense (K, N)
+    float32 CUDA tensor.  Returns (BT (W, N) float32, DT (W, N/32) int32) on the device."""
+    torch = _torch()
+    K, N = dense.shape
+    W = K // 32 * n_keep
+    BT = torch.empty((W, N), dtype=torch.float32, device=dense.device)
+    DT = torch.empty((W, N // 32), dtype=torch.int32, device=dense.device)
+    _check("nmspmm_prune_device",
+           load_library().nmspmm_prune_device(_dev_ptr(dense, torch.float32, "dense"), BT.data_ptr(), DT.data_ptr(),
+                                              K, N, n_keep, vec_len, _stream_ptr(stream)))
+    return BT, DT
+
+
 def gemm_gather(desc: GemmDesc, A, B, D, column_info, out_ptrs, ldc: int, col0: int, workspace=None, stream=None) -> None:
     """nmspmm_gemm_gather: the multiply of one rank's column slab, its finished tiles stored
     into every buffer of ``out_ptrs`` (device addresses as ints: this rank's full-width C and
@@ -358,6 +373,13 @@ class NMSpMM:
     @classmethod
     def from_problem(cls, p: "formats.NMProblem", layout_ns: int = 128, fmt: Optional[int] = None, device=None):
         return cls(p.BT, p.DT, p.K, p.n_keep, layout_ns, fmt, device)
+
+    @classmethod
+    def from_dense(cls, dense, n_keep: int, vec_len: int = 32, layout_ns: int = 128, fmt: Optional[int] = None):
+        """Prune a dense (K, N) float32 CUDA weight to ``n_keep``:32 by per-vector L2 magnitude,
+        compress and pack it, all on the device (prune_device, then the packing kernels)."""
+        BT, DT = prune_device(dense, n_keep, vec_len)
+        return cls(BT, DT, dense.shape[0], n_keep, layout_ns, fmt, dense.device)
 
     def desc(self, M: int, path: int = PATH_FP32, split_k: int = 0, tile: int = 0) -> GemmDesc:
         return make_desc(M, self.N, self.K, self.n_keep, self.format, self.layout_ns, path, split_k, tile)

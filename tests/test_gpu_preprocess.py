@@ -82,3 +82,37 @@ def test_deep_k_packing_bit_exact_full_size(pkg, orc):
     Dm = wantD.reshape(N // Ns, DT2.shape[0], Qs)
     blk, w, q = 3, 1234, 2
     assert cim[blk, w // pn, Dm[blk, w, q]] == DT2[w, blk * Qs + q]
+
+
+@pytest.mark.parametrize("n_keep", [4, 8, 12, 16, 32])
+@pytest.mark.parametrize("vec_len", [32, 64])
+def test_prune_device_matches_the_host_generator(pkg, n_keep, vec_len):
+    """Magnitude pruning on the GPU: kept rows and values equal, bit for bit, to the host
+    generator's (formats.prune_magnitude), including ties (equal rows keep the lower one)."""
+    rng = np.random.default_rng(300 + n_keep)
+    K, N = 256, 384
+    Bd = (rng.standard_normal((K, N)) * 0.02).astype(np.float32)
+    Bd[5] = Bd[3]                       # ties inside a window
+    Bd[40:44, :64] = Bd[36:40, :64]
+    Bd[64:96, 128:192] = 0.0            # a window of one vector that is all ties
+    BT, DT = pkg.prune_device(torch.from_numpy(Bd).cuda(), n_keep, vec_len)
+    want_BT, want_DT = pkg.formats.prune_magnitude(Bd, n_keep, vec_len)
+    assert np.array_equal(DT.cpu().numpy(), want_DT)
+    assert np.array_equal(BT.cpu().numpy(), want_BT)
+
+
+def test_from_dense_runs_prune_pack_and_multiply_on_the_device(pkg, orc):
+    p = pkg.formats.make_llm_linear(64, N=1408, K=1024, n_keep=8, seed=77)
+    Bd = pkg.formats.normal(77, 2, 1024 * 1408, std=0.02).reshape(1024, 1408)
+    op = pkg.NMSpMM.from_dense(torch.from_numpy(Bd).cuda(), 8)
+    C = op.matmul(torch.from_numpy(p.A_km).cuda()).cpu().numpy()
+    want = orc.nm_gemm_f32(p.A_km, p.B_col, p.D_col)
+    assert np.linalg.norm(C - want) / np.linalg.norm(want) <= 1e-5
+
+
+def test_prune_device_rejects_bad_shapes(pkg):
+    x = torch.zeros((48, 64), device="cuda")
+    with pytest.raises(pkg.NMSpMMError):
+        pkg.prune_device(x, 8)                          # K not a multiple of 32
+    with pytest.raises(pkg.NMSpMMError):
+        pkg.prune_device(torch.zeros((64, 96), device="cuda"), 8, 64)    # N not a multiple of the vector width
