@@ -13,7 +13,10 @@
 //   * a launcher whose SPLIT_K resolves above 1 allocates scratch once per host
 //     thread (the reference signatures carry no workspace argument);
 //   * the CTA tile is chosen by the library, the entry point only selects the index
-//     layout (Ns = 128 / 64 / 64 / 32 for huge / large / medium / small).
+//     layout (Ns = 128 / 64 / 64 / 32 for huge / large / medium / small);
+//   * the arithmetic is exact FP32 unless the environment variable NMSPMM_PATH=tf32 is set
+//     before the first launcher call: then the launchers use the TF32 tensor-core path
+//     (about 2e-3 relative error instead of 1e-6; the signatures have no argument for it).
 // The C-ABI underneath is include/nmspmm_b200.h.
 #ifndef NMSpMM_H
 #define NMSpMM_H

@@ -5,6 +5,8 @@
 // 584-585); other failures are reported on stderr.
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
+#include <cstring>
 
 #include "NM-SpMM.h"
 #include "nmspmm_b200.h"
@@ -12,6 +14,18 @@
 namespace {
 
 bool near(float a, float b) { return std::fabs(a - b) < 1e-6f; }
+
+// The reference's signatures carry no choice of arithmetic.  A program linked against this
+// library without source changes selects the tensor-core path by setting the environment
+// variable NMSPMM_PATH=tf32 before its first launcher call (anything else: exact FP32).
+int dropin_path()
+{
+    static const int path = [] {
+        const char* v = std::getenv("NMSPMM_PATH");
+        return (v && (std::strcmp(v, "tf32") == 0 || std::strcmp(v, "TF32") == 0)) ? NMSPMM_PATH_TF32 : NMSPMM_PATH_FP32;
+    }();
+    return path;
+}
 
 void report(const char* who, int rc)
 {
@@ -36,7 +50,7 @@ void launch_low(const char* who, int layout_ns, float* A, float* B, int* D, floa
     } else {
         return;                                  // the reference launches nothing for other values
     }
-    nmspmm_gemm_desc d = { M, N, K, n_keep, NMSPMM_FORMAT_LOW, layout_ns, NMSPMM_PATH_FP32, SPLIT_K > 1 ? SPLIT_K : 0, 0 };
+    nmspmm_gemm_desc d = { M, N, K, n_keep, NMSPMM_FORMAT_LOW, layout_ns, dropin_path(), SPLIT_K > 1 ? SPLIT_K : 0, 0 };
     report(who, nmspmm_gemm_with_cached_workspace(&d, A, B, D, nullptr, C, nullptr));
 }
 
@@ -55,7 +69,7 @@ void launch_high(const char* who, int layout_ns, float* A, float* B, int* D, int
     } else {
         return;
     }
-    nmspmm_gemm_desc d = { M, N, K, n_keep, NMSPMM_FORMAT_HIGH, layout_ns, NMSPMM_PATH_FP32, SPLIT_K > 1 ? SPLIT_K : 0, 0 };
+    nmspmm_gemm_desc d = { M, N, K, n_keep, NMSPMM_FORMAT_HIGH, layout_ns, dropin_path(), SPLIT_K > 1 ? SPLIT_K : 0, 0 };
     report(who, nmspmm_gemm_with_cached_workspace(&d, A, B, D, column_info, C, nullptr));
 }
 

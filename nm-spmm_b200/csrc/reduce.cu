@@ -14,6 +14,31 @@
 
 namespace nmspmm {
 
+// The reduction kernels are launched with programmatic stream serialisation: the launch is
+// set up while the multiply still runs and the grid starts as soon as the multiply's last
+// CTA has exited, instead of a launch latency later (these launches follow multiplies that
+// last 15-100 us).  This wait is what orders the reads below after the multiply's writes.
+__device__ __forceinline__ void wait_for_the_multiply()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_after_multiply(void (*kernel)(KArgs...), unsigned blocks, unsigned threads, cudaStream_t st, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 // Thread-fragment map of the FFMA kernels' accumulators for a tile MS x NS with warp tile
 // WM x 32: thread tid holds rows row(i), i < MT, and columns col0 .. col0 + 3 and
 // col0 + 16 .. col0 + 19 of them; the slot stores fragment row i as float4 words
@@ -41,6 +66,7 @@ nm_reduce_pieces_kernel(const GemmArgs g, const GemmOutputs outs, int first_tile
     constexpr size_t kSlot = static_cast<size_t>(2 * MT) * NCT;       // float4 words per slot
     const int tile = first_tile + blockIdx.x / MT, i = blockIdx.x % MT;
     const int tid = threadIdx.x;
+    wait_for_the_multiply();
     int v_first, v_last;
     tile_contributors(g.sched, tile, v_first, v_last);
     if (v_first == v_last) return;                         // one range held the whole tile and stored it
@@ -80,8 +106,7 @@ template <int MS, int NS, int WM>
 static cudaError_t launch_reduce(const GemmArgs& a, const GemmOutputs& outs, int first_tile, int n_tiles, cudaStream_t st)
 {
     using Map = FragmentMap<MS, NS, WM>;
-    nm_reduce_pieces_kernel<MS, NS, WM><<<n_tiles * Map::MT, Map::NCT, 0, st>>>(a, outs, first_tile);
-    return cudaGetLastError();
+    return launch_after_multiply(nm_reduce_pieces_kernel<MS, NS, WM>, n_tiles * Map::MT, Map::NCT, st, a, outs, first_tile);
 }
 
 cudaError_t launch_reduce_pieces(int tile_id, const GemmArgs& a, const GemmOutputs& outs, int first_tile, int n_tiles, cudaStream_t st)
@@ -108,6 +133,7 @@ __global__ void __launch_bounds__(256) nm_reduce_slices_kernel(const GemmArgs g,
     const int ty = tile / g.tiles_x, tx = tile - ty * g.tiles_x;
     const int bi = ty * MS, bj = tx * NS;
     const int S = g.sched.split_k;
+    wait_for_the_multiply();
     const float4* slots = reinterpret_cast<const float4*>(g.partial) + static_cast<size_t>(tile) * S * (MS * V4);
     for (int e = threadIdx.x; e < ROWS * V4; e += 256) {
         const int row = r0 + e / V4, c4 = e % V4;
@@ -131,10 +157,9 @@ __global__ void __launch_bounds__(256) nm_reduce_slices_kernel(const GemmArgs g,
 cudaError_t launch_reduce_slices(int ns, const GemmArgs& a, const GemmOutputs& outs, cudaStream_t st)
 {
     const int blocks = a.sched.n_tiles * (128 / 16);
-    if (ns == 256) nm_reduce_slices_kernel<256><<<blocks, 256, 0, st>>>(a, outs);
-    else if (ns == 128) nm_reduce_slices_kernel<128><<<blocks, 256, 0, st>>>(a, outs);
-    else return cudaErrorInvalidValue;
-    return cudaGetLastError();
+    if (ns == 256) return launch_after_multiply(nm_reduce_slices_kernel<256>, blocks, 256, st, a, outs);
+    if (ns == 128) return launch_after_multiply(nm_reduce_slices_kernel<128>, blocks, 256, st, a, outs);
+    return cudaErrorInvalidValue;
 }
 
 }  // namespace nmspmm
