@@ -54,13 +54,15 @@ __global__ void __launch_bounds__(256) preprocess_high_kernel(const int* __restr
                                                               int* __restrict__ cinfo, int pm, int pn, int W, int Q,
                                                               int Qs, int fuse)
 {
-    extern __shared__ int rows[];                  // [pn][kHighBlocksPerCta * Qs]
+    extern __shared__ int rows[];                  // [pn][kHighBlocksPerCta * Qs + Qs]: padded, see pitch
     const int win = blockIdx.x;
     const int blk0 = blockIdx.y * kHighBlocksPerCta;
     const int nblk_total = Q / Qs;
     const int nblk = min(kHighBlocksPerCta, nblk_total - blk0);
     const int width = nblk * Qs;                   // ints per row held here
-    const int pitch = kHighBlocksPerCta * Qs;
+    // a warp reads one block's [pn][Qs] indices, Qs from each row: Qs extra ints per row
+    // put consecutive rows Qs banks apart (an unpadded pitch made that an 8-way conflict)
+    const int pitch = kHighBlocksPerCta * Qs + Qs;
     for (int t = threadIdx.x; t < pn * width; t += blockDim.x) {
         const int x = t / width, c = t % width;
         int v = DT[static_cast<size_t>(win * pn + x) * Q + blk0 * Qs + c];
@@ -125,7 +127,7 @@ cudaError_t launch_preprocess_high(const int* DT, int* D, int* cinfo, int pm, in
     if (W == 0 || Q == 0) return cudaSuccess;
     const int nblk = Q / Qs, nwin = W / pn;
     dim3 grid(nwin, (nblk + kHighBlocksPerCta - 1) / kHighBlocksPerCta);
-    const size_t smem = static_cast<size_t>(pn) * kHighBlocksPerCta * Qs * sizeof(int);
+    const size_t smem = static_cast<size_t>(pn) * (kHighBlocksPerCta * Qs + Qs) * sizeof(int);
     preprocess_high_kernel<<<grid, 256, smem, st>>>(DT, D, cinfo, pm, pn, W, Q, Qs, fuse);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
