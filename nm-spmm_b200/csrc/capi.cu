@@ -156,24 +156,37 @@ static int make_plan(const nmspmm_gemm_desc* d, int sms, Plan* p)
         const long long nt = static_cast<long long>(p->tiles_x) * p->tiles_y;
         if (nt >= (1LL << 26)) return NMSPMM_UNSUPPORTED;
         p->n_tiles = static_cast<int>(nt);
-        // K slices: the caller's number, or as many as fill the resident CTA slots with
-        // slices of at least four windows when the tiles alone do not.
+        // K slices.  The caller's number applies to every tile.  Otherwise: tiles that fill
+        // complete waves of resident CTAs run whole; the tiles of the partial last wave (all
+        // tiles of a small problem) are cut into as many slices, of at least four windows,
+        // as the free CTA slots allow -- with one CTA per SM a last wave that is 46 % full
+        // (512 tiles on 148 SMs) otherwise costs as much as a full one.
         const int resident = sms * (want_ns == 256 ? 1 : 2);
-        long long s = d->split_k;
+        long long s = d->split_k, whole = 0;
         if (s <= 0) {
-            s = resident / nt;
+            whole = nt / resident * resident;
+            const long long tail = nt - whole;
+            s = tail > 0 ? resident / tail : 1;
             if (s > p->n_win / 4) s = p->n_win / 4;
+            if (s > 16) s = (nt < resident) ? s : 16;
+            // with two CTAs per SM a partial last wave is cheap (the lone CTA of an SM runs
+            // faster) and slicing it measured 3 % slower: leave it whole
+            if (want_ns == 128 && whole > 0) s = 1;
+            if (s < 2) { s = 1; whole = nt; }
         }
         if (s > p->n_win) s = p->n_win;
         if (s < 1) s = 1;
-        if (nt * s >= (1LL << 30)) return NMSPMM_UNSUPPORTED;
+        if (s == 1) whole = nt;
+        const long long sliced_tiles = nt - whole;
+        if (whole + sliced_tiles * s >= (1LL << 30)) return NMSPMM_UNSUPPORTED;
         p->split_k = static_cast<int>(s);
-        p->n_dp = (s == 1) ? p->n_tiles : 0;
-        p->n_virtual = p->grid = static_cast<int>(nt * s);
-        if (s > 1) {
-            p->slots = p->n_virtual;
+        p->n_dp = static_cast<int>(whole);
+        p->n_virtual = p->grid = static_cast<int>(whole + sliced_tiles * s);
+        if (sliced_tiles > 0) {
+            p->slots = static_cast<int>(sliced_tiles * s);
             p->deferred = true;
-            p->n_split_tiles = p->n_tiles;
+            p->first_split_tile = p->n_dp;
+            p->n_split_tiles = static_cast<int>(sliced_tiles);
             p->partial_bytes = static_cast<size_t>(p->slots) * 128 * want_ns * sizeof(float);
         }
         return NMSPMM_OK;
@@ -526,7 +539,8 @@ static int gemm_launch(const nmspmm_gemm_desc* desc, const float* A_dev, const f
                         : p.tv->launch(a, outs, p.grid, static_cast<cudaStream_t>(stream));
     if (e == cudaSuccess && p.v && p.slots > 0 && p.deferred)
         e = launch_reduce_pieces(p.v->tile_id, a, outs, p.first_split_tile, p.n_split_tiles, static_cast<cudaStream_t>(stream));
-    if (e == cudaSuccess && p.tv && p.split_k > 1) e = launch_reduce_slices(p.tv->ns, a, outs, static_cast<cudaStream_t>(stream));
+    if (e == cudaSuccess && p.tv && p.slots > 0)
+        e = launch_reduce_slices(p.tv->ns, a, outs, p.first_split_tile, p.n_split_tiles, static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? NMSPMM_OK : cuda_fail(e);
 }
 

@@ -125,14 +125,19 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
     const uint32_t tmem_word = bar_acc + 8, abort_word = tmem_word + 4;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // One CTA per (tile, K slice): with split_k slices per tile the accumulators go to
-    // the slice's scratch slot and the reduction kernel adds the slots.
-    const int n_slices = g.sched.split_k > 1 ? g.sched.split_k : 1;
-    const int tile = blockIdx.x / n_slices;
+    // The first n_dp CTAs take one whole tile each.  The remaining tiles (the partial last
+    // wave of a large problem, or all tiles of a small one) are cut into split_k K slices,
+    // one CTA each: a slice's accumulators go to its scratch slot and the reduction kernel
+    // adds the slots.
+    const int n_dp = g.sched.n_dp;
+    const bool sliced = static_cast<int>(blockIdx.x) >= n_dp;
+    const int n_slices = sliced ? g.sched.split_k : 1;
+    const int slot = static_cast<int>(blockIdx.x) - n_dp;  // scratch slot of a sliced CTA
+    const int tile = sliced ? n_dp + slot / n_slices : static_cast<int>(blockIdx.x);
     const int ty = tile / g.tiles_x, tx = tile - ty * g.tiles_x;
     const int bi = ty * MS, bj = tx * NS;
     int win0, n_win;                                       // this CTA's k windows: win0 .. win0 + n_win - 1
-    slice_range(g.sched.n_win, n_slices, blockIdx.x - tile * n_slices, win0, n_win);
+    slice_range(g.sched.n_win, n_slices, sliced ? slot % n_slices : 0, win0, n_win);
     const int live_vecs = min(QT, (g.N - bj) / 32);        // vectors of the tile that exist
     const int qs_shift = g.qs_shift, layout_shift = qs_shift + 5;
     const int d_chunk = WS << qs_shift;
@@ -319,8 +324,8 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
                 uint32_t v[32];
                 tmem_ld_x32(tmem_addr(tmem, quad * 32, col), v);
                 tmem_wait_ld();
-                if (n_slices > 1) {
-                    float4* dst = reinterpret_cast<float4*>(g.partial + (static_cast<size_t>(blockIdx.x) * MS + row) * NS + col);
+                if (sliced) {
+                    float4* dst = reinterpret_cast<float4*>(g.partial + (static_cast<size_t>(slot) * MS + row) * NS + col);
 #pragma unroll
                     for (int x = 0; x < 8; ++x)
                         dst[x] = make_float4(__uint_as_float(v[4 * x]), __uint_as_float(v[4 * x + 1]),

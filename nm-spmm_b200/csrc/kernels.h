@@ -50,9 +50,10 @@ extern const int kTf32VariantCount;
 cudaError_t launch_reduce_pieces(int tile_id, const GemmArgs& args, const GemmOutputs& outs, int first_tile, int n_tiles,
                                  cudaStream_t st);
 
-// Adds the K slices the tensor-core multiply (tile 128 x ns, args.sched.split_k > 1)
-// left in scratch and writes C.
-cudaError_t launch_reduce_slices(int ns, const GemmArgs& args, const GemmOutputs& outs, cudaStream_t st);
+// Adds the K slices the tensor-core multiply (tile 128 x ns) left in scratch for the tiles
+// first_tile .. first_tile + n_tiles - 1 (args.sched.split_k slices each) and writes C.
+cudaError_t launch_reduce_slices(int ns, const GemmArgs& args, const GemmOutputs& outs, int first_tile, int n_tiles,
+                                 cudaStream_t st);
 
 // packed = 0: scalar FFMA loop; 1: two-lane packed FFMA2 loop.
 cudaError_t measure_ffma_peak(double* tflops, int packed, cudaStream_t st);

@@ -122,19 +122,20 @@ cudaError_t launch_reduce_pieces(int tile_id, const GemmArgs& a, const GemmOutpu
     }
 }
 
-// The tensor-core path's K slices: slot (tile * split_k + z) holds the slice's 128 x NS
-// accumulator tile row-major.  One CTA adds the slices of 16 rows of a tile, in ascending
+// The tensor-core path's K slices: the tiles from first_tile on are sliced; slot
+// ((tile - first_tile) * split_k + z) holds a slice's 128 x NS accumulator tile row-major.  One CTA adds the slices of 16 rows of a tile, in ascending
 // k order, and writes the rows and columns of C that exist.
 template <int NS>
-__global__ void __launch_bounds__(256) nm_reduce_slices_kernel(const GemmArgs g, const GemmOutputs outs)
+__global__ void __launch_bounds__(256) nm_reduce_slices_kernel(const GemmArgs g, const GemmOutputs outs, int first_tile)
 {
     constexpr int MS = 128, ROWS = 16, V4 = NS / 4;        // float4 words per tile row
-    const int tile = blockIdx.x / (MS / ROWS), r0 = (blockIdx.x % (MS / ROWS)) * ROWS;
+    const int sliced_tile = blockIdx.x / (MS / ROWS), r0 = (blockIdx.x % (MS / ROWS)) * ROWS;
+    const int tile = first_tile + sliced_tile;
     const int ty = tile / g.tiles_x, tx = tile - ty * g.tiles_x;
     const int bi = ty * MS, bj = tx * NS;
     const int S = g.sched.split_k;
     wait_for_the_multiply();
-    const float4* slots = reinterpret_cast<const float4*>(g.partial) + static_cast<size_t>(tile) * S * (MS * V4);
+    const float4* slots = reinterpret_cast<const float4*>(g.partial) + static_cast<size_t>(sliced_tile) * S * (MS * V4);
     for (int e = threadIdx.x; e < ROWS * V4; e += 256) {
         const int row = r0 + e / V4, c4 = e % V4;
         if (bi + row >= g.M || bj + c4 * 4 >= g.N) continue;
@@ -154,11 +155,12 @@ __global__ void __launch_bounds__(256) nm_reduce_slices_kernel(const GemmArgs g,
     }
 }
 
-cudaError_t launch_reduce_slices(int ns, const GemmArgs& a, const GemmOutputs& outs, cudaStream_t st)
+cudaError_t launch_reduce_slices(int ns, const GemmArgs& a, const GemmOutputs& outs, int first_tile, int n_tiles, cudaStream_t st)
 {
-    const int blocks = a.sched.n_tiles * (128 / 16);
-    if (ns == 256) return launch_after_multiply(nm_reduce_slices_kernel<256>, blocks, 256, st, a, outs);
-    if (ns == 128) return launch_after_multiply(nm_reduce_slices_kernel<128>, blocks, 256, st, a, outs);
+    const int blocks = n_tiles * (128 / 16);
+    if (blocks <= 0) return cudaSuccess;
+    if (ns == 256) return launch_after_multiply(nm_reduce_slices_kernel<256>, blocks, 256, st, a, outs, first_tile);
+    if (ns == 128) return launch_after_multiply(nm_reduce_slices_kernel<128>, blocks, 256, st, a, outs, first_tile);
     return cudaErrorInvalidValue;
 }
 

@@ -116,10 +116,13 @@ def test_split_k_fills_the_machine_for_skinny_shapes(pkg):
     info = pkg.plan(tdeep)
     assert info.tile_n == 128 and info.split_k == 296 // 8 and info.grid == 8 * info.split_k
     assert pkg.workspace_bytes(tdeep) == info.grid * 128 * 128 * 4
+    # 512 tiles on 148 one-CTA SMs: three whole waves, the 68 tiles of the last one in two slices each
     tbig = pkg.plan(pkg.make_desc(4096, 4096, 4096, 8, 1, 128, path=pkg.PATH_TF32))
-    assert tbig.tile_n == 256 and tbig.split_k == 1 and tbig.grid == 512
+    assert tbig.tile_n == 256 and tbig.n_dp == 444 and tbig.split_k == 2 and tbig.grid == 444 + 2 * 68
     tlow = pkg.plan(pkg.make_desc(4096, 4096, 4096, 16, 0, 128, path=pkg.PATH_TF32))
-    assert tlow.tile_n == 128 and tlow.split_k == 1 and tlow.grid == 1024
+    assert tlow.tile_n == 128 and tlow.split_k == 1 and tlow.grid == 1024      # two CTAs per SM: the last wave stays whole
+    texact = pkg.plan(pkg.make_desc(128 * 148, 256, 4096, 8, 1, 128, path=pkg.PATH_TF32))    # exactly one wave: nothing to slice
+    assert texact.split_k == 1 and texact.grid == 148 and pkg.workspace_bytes(pkg.make_desc(128 * 148, 256, 4096, 8, 1, 128, path=pkg.PATH_TF32)) == 0
     one = pkg.plan(pkg.make_desc(128, 128, 64, 16, 0, 128, split_k=1))
     assert one.split_k == 1 and pkg.workspace_bytes(pkg.make_desc(128, 128, 64, 16, 0, 128, split_k=1)) == 0
 
