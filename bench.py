@@ -410,8 +410,24 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                                      if world > 1 else [])
     for name, gather in modes:
         fn = lambda i, g=gather: sh.matmul(LA, gather=g)
-        for i in range(2):
-            fn(i)
+        # the gathers are optional extras of the path: a set-up failure on one rank (peer
+        # mapping, NCCL) must not take the headline line down, and every rank must agree
+        # on whether the mode runs at all
+        ok = 1.0
+        try:
+            for i in range(2):
+                fn(i)
+            torch.cuda.synchronize()
+        except Exception as exc:      # noqa: BLE001
+            ok, why = 0.0, f"{type(exc).__name__}: {exc}"[:200]
+        if world > 1:
+            flag = torch.tensor([ok], dtype=torch.float64, device="cuda")
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if float(flag.item()) == 0.0:
+                large[name] = {"unavailable": why if ok == 0.0 else "failed on another rank"}
+                continue
+        elif ok == 0.0:
+            raise RuntimeError(why)
         t = max_over_ranks(time_steps(torch, fn, l_steps, barrier)) / l_steps
         large[name] = {"ms": t, "useful_tflops": l_useful / (t * 1e-3) / 1e12}
     if pkg.device_status() != 0:
