@@ -55,7 +55,8 @@ template <int MS, int NS, int WM, int WS, int KS_, int MODE>
 struct FfmaCfg {
     static constexpr int KS = KS_;                       // rows of A staged per window: 32, or 64 (a merged HIGH window)
     static constexpr bool HALF = (MODE == kModeHigh && KS_ == 32);   // HIGH staged by halves of the merged window
-    static_assert(MODE == kModeHigh || KS_ == 32, "LOW windows are 32 k wide");
+    static constexpr bool PAIR = (MODE == kModeLow && KS_ == 64);    // LOW staged as pairs of 32-k windows (WS = 2 n_keep)
+    static_assert(MODE == kModeHigh || KS_ == 32 || KS_ == 64, "LOW windows are 32 k wide, staged singly or in pairs");
     static constexpr int QT = NS / kVecLen;              // vectors per tile
     static constexpr int WARPS_M = MS / WM;
     static constexpr int NCW = QT * WARPS_M;             // warps (all of them compute)
@@ -238,6 +239,7 @@ __device__ __forceinline__ void nm_gemm_ffma_body(const GemmArgs& g, const CUten
                 if (lane < WS) {
                     int k = lds_s32(st + d_rel);
                     if constexpr (MODE == kModeHigh) k = lds_s32(st + ci_rel + k * 4) - half_base;
+                    if constexpr (Cfg::PAIR) k += (lane >= WS / 2) ? 32 : 0;       // second window of the pair
                     my_off = k * (MS * 4);
                 }
 #define NMSPMM_OFF(p) __shfl_sync(0xffffffffu, my_off, (p))
@@ -250,7 +252,7 @@ __device__ __forceinline__ void nm_gemm_ffma_body(const GemmArgs& g, const CUten
                     for (int p = 0; p < WS; ++p) row_off[p] = lds_s32(st + ci_rel + row_off[p] * 4) - half_base;
                 }
 #pragma unroll
-                for (int p = 0; p < WS; ++p) row_off[p] *= (MS * 4);
+                for (int p = 0; p < WS; ++p) row_off[p] = (row_off[p] + ((Cfg::PAIR && p >= WS / 2) ? 32 : 0)) * (MS * 4);
 #define NMSPMM_OFF(p) row_off[(p)]
 #endif
 
