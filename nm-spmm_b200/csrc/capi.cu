@@ -232,7 +232,12 @@ static int make_plan(const nmspmm_gemm_desc* d, int sms, Plan* p)
         // (With two or more complete waves the whole-tile grid is used as it is: measured
         // on 4096^3, the partial last wave costs less than the split tiles' round trip
         // through scratch, because a CTA that has an SM to itself runs faster.)
-        const long long n_dp = (n_tiles >= 2LL * resident) ? n_tiles : n_tiles / resident * resident;
+        // Unless that last wave is nearly empty (under a quarter of the CTA slots): then its
+        // few tiles would each hold an SM for a whole tile's time, and cutting them over all
+        // the slots pays (8192 x 3584 x 8192, one rank's slab of eight: 1792 tiles = 6.05 waves).
+        const long long full_waves = n_tiles / resident * resident;
+        const bool sparse_tail = (n_tiles - full_waves) * 4 <= resident;
+        const long long n_dp = (n_tiles >= 2LL * resident && !sparse_tail) ? n_tiles : full_waves;
         const long long tail_tiles = n_tiles - n_dp;
         long long n_sk = 0;
         if (tail_tiles > 0) {

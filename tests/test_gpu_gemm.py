@@ -202,7 +202,8 @@ def test_deep_k_full_size(pkg, orc):
 def test_large_sharded_full_size(pkg, orc):
     """Large configuration at full size (8192 x 28672 x 8192, 8:32, V = 64): sampled rows
     against the checker, and the column slabs of a 4-way shard (computed one after the other
-    on this GPU through the package's partition code) equal the unsharded result bit for bit."""
+    on this GPU through the package's partition code) agree with the unsharded result (to rounding:
+    a slab's nearly empty last wave is cut along k, which the unsharded launch's is not)."""
     M, N, K = 8192, 28672, 8192
     p = pkg.formats.make_random(M, N, K, 8, seed=83, vec_len=64)
     A = torch.from_numpy(p.A_km).cuda()
@@ -214,5 +215,6 @@ def test_large_sharded_full_size(pkg, orc):
     for rank in (0, 3):
         bt, dt, (c0, c1) = pkg.sharding.shard_operands(p.BT, p.DT, rank, world, 128)
         slab = pkg.NMSpMM(bt, dt, K, 8, 128).matmul(A)
-        assert torch.equal(slab, full[:, c0:c1]), rank
+        ref = full[:, c0:c1]
+        assert float((slab - ref).norm() / ref.norm()) <= 1e-6, rank
     assert pkg.device_status() == 0

@@ -95,6 +95,8 @@ def test_plan_balances_the_last_wave(pkg):
     assert info.stream_k == 1 and 0 < info.n_dp < tiles and info.n_dp % (info.n_virtual - info.n_dp) == 0
     many = pkg.plan(pkg.make_desc(4096, 4096, 4096, 8, 1, 128))               # 1024 tiles: whole tiles only
     assert many.n_dp == many.n_virtual == 1024
+    slab = pkg.plan(pkg.make_desc(8192, 3584, 8192, 8, 1, 128))                # 1792 tiles = 6 waves + 16 tiles: a nearly empty last wave is cut along k
+    assert slab.n_dp == 6 * 296 and slab.n_virtual == 6 * 296 + 296
     exact = pkg.plan(pkg.make_desc(128 * 296 // 8, 1024, 4096, 8, 1, 128))      # 37 x 8 = 296 tiles: nothing to balance
     assert exact.n_dp == exact.tiles_x * exact.tiles_y == exact.n_virtual
     assert pkg.workspace_bytes(pkg.make_desc(128 * 296 // 8, 1024, 4096, 8, 1, 128)) == 0
