@@ -142,7 +142,7 @@ static int make_plan(const nmspmm_gemm_desc* d, int sms, Plan* p)
         // at 4096^3: 0.233 against 0.266 ms at 8:32, 0.166 against 0.232 ms at 4:32), tile
         // 128 x 128 with two CTAs per SM for the 32-k window formats (0.360 against 0.424 ms
         // at 16:32); the caller's tile wins over both.
-        int want_ns = (mode == kModeHigh && ((d->N + 255) / 256) * ((d->M + 127) / 128) >= sms) ? 256 : 128;
+        int want_ns = (((d->N + 255) / 256) * ((d->M + 127) / 128) >= sms) ? 256 : 128;
         if (d->tile == kTile128x256) want_ns = 256;
         if (d->tile == kTile128x128) want_ns = 128;
         for (int i = 0; i < kTf32VariantCount; ++i)
@@ -151,7 +151,7 @@ static int make_plan(const nmspmm_gemm_desc* d, int sms, Plan* p)
         if (!p->tv) return NMSPMM_UNSUPPORTED;
         p->ws = p->tv->ws;
         p->W = d->K / 32 * d->n_keep;
-        if (p->W % p->ws != 0) return NMSPMM_UNSUPPORTED;   // 12:32 is staged as window pairs: K % 64 == 0
+        if (p->W % p->ws != 0) return NMSPMM_UNSUPPORTED;
         p->n_win = p->W / p->ws;
         p->tiles_x = (d->N + p->tv->ns - 1) / p->tv->ns;
         p->tiles_y = (d->M + 127) / 128;
@@ -496,7 +496,7 @@ int nmspmm_gemm_plan(const nmspmm_gemm_desc* desc, nmspmm_gemm_plan_info* out)
     out->n_virtual = p.n_virtual;
     out->grid = p.grid;
     out->stream_k = p.split_k > 0 ? 0 : 1;
-    out->threads = p.v ? p.v->threads : 320;
+    out->threads = p.v ? p.v->threads : p.tv->threads;
     out->smem_bytes = p.v ? p.v->smem_bytes : p.tv->smem_bytes;
     out->stages = p.v ? p.v->stages : p.tv->stages;
     return NMSPMM_OK;

@@ -174,6 +174,37 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void* tenso
         : "memory");
 }
 
+// Tiled 3-D tensor copy global -> shared ({x, y, z} = element coordinates of the box corner).
+__device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tensor_map, int x, int y, int z, uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tensor_map)), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
+// One thread's asynchronous 4-byte copy global -> shared (cp.async groups of the issuing thread).
+__device__ __forceinline__ void cp_async_4(uint32_t dst_smem, const void* src_gmem)
+{
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst_smem), "l"(src_gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void sts_f32(uint32_t addr, float v)
+{
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void sts_s32(uint32_t addr, int v)
+{
+    asm volatile("st.shared.s32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void sts_f4(uint32_t addr, float4 v)
+{
+    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+
 // Shared-memory loads by 32-bit shared address.  volatile: they stay behind the
 // mbarrier wait that guards the stage they read.
 __device__ __forceinline__ float4 lds_f4(uint32_t addr)

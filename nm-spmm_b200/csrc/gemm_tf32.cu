@@ -1,27 +1,43 @@
 // TF32 tensor-core path of the vector-wise N:M sparse GEMM (tcgen05, accumulators in TMEM).
 //
-// One CTA computes a 128 x NS tile of C (NS / 32 vectors of 32 columns) over all k windows.
-// The dense contraction here is per vector: C[128 x 32] += A_gathered[128 x WS] . B[WS x 32],
-// and A_gathered differs for every vector, so the gather cannot be expressed by a shared-
-// memory descriptor.  It is done on chip instead:
-//   warp 0      TMA producer: per window one tiled copy of the dense A window (As[KS][128],
-//               unswizzled), one swizzled tiled copy per vector of its WS x 32 block of B
-//               (32-byte chunks swizzled within 128-byte rows: the one legal layout of an
-//               MN-major TF32 operand), bulk copies of the packed indices and column lists.
-//   warps 2-17  sixteen gather warps in two groups that take the windows in turn (one group's
-//               waits overlap the other's copying, which keeps shared memory busy); within
-//               a group four warps (one per TMEM lane quadrant) work on one vector.  Thread
-//               = row of the tile.  Lane p of a warp resolves the vector's
-//               p-th index to a row of As; the offsets go round by shuffle; every thread
-//               reads its row's WS gathered values from As (conflict-free: consecutive lanes,
-//               consecutive words) and stores them as WS TMEM columns with one tcgen05.st
-//               per 16: the A operand of WS / 8 MMAs.  All vectors of a window share one
-//               A buffer in TMEM and one hand-off; the buffers form a ring.
-//   warp 1      one elected thread issues the window's tcgen05.mma kind::tf32 (M128 N32 K8,
-//               A from TMEM, B from shared memory, D = the vector's 32 accumulator columns)
-//               back to back and commits to the mbarriers that hand the A buffer and the
-//               stage back.
-//   epilogue    the gather warps read the accumulators (tcgen05.ld) and store C.
+// One CTA computes a 128 x NS tile of C (QT = NS / 32 vectors of 32 columns) over its k steps.
+// A step is one 32-k window (one 64-k merged window for 4:32) with WS kept rows of B.  The
+// contraction is per vector, C[128 x 32] += A_gathered[128 x WS] . B[WS x 32], and A_gathered
+// (the WS columns of the step's A window that the vector's index list names) differs for
+// every vector.  The gather itself is done by the tensor core:
+//
+//     G[128 x QT*WS] = A_window[128 x KW] . P[KW x QT*WS]
+//
+// where column (v, j) of P is one-hot at the k that vector v's j-th index names.  Products
+// with 1.0 and sums with 0.0 are exact, so G holds exactly the (TF32-truncated) gathered
+// values -- in Tensor Memory, lane = tile row, column = (v, j): the layout of a TMEM A
+// operand.  The second instruction group then multiplies, per vector, G's WS columns by the
+// vector's WS x 32 block of B.  Nothing of A goes through registers; the only generic-proxy
+// shared-memory traffic of the main loop is two 4-byte stores per index (clear the old
+// one-hot entry, set the new one).  Tensor work is twice the useful work for every ratio.
+// A non-finite value anywhere in a row of the A window reaches every gathered column of that
+// row (0 x inf), not only the vectors that select it: this path wants finite A.
+//
+//   warp 0      TMA producer: per step one tiled copy of the A window and one of the B rows,
+//               both as blocks of 32 floats along m / n with 32-byte chunks swizzled within
+//               128-byte rows (the one legal layout of an MN-major TF32 operand).
+//   warp 1      one elected thread issues the gathers (tcgen05.mma kind::tf32, A and P from
+//               shared memory, M128 N=QT*WS, KW/8 instructions per step) into a ring of
+//               result buffers in TMEM, each followed by a tcgen05.commit to the buffer's
+//               mbarrier.
+//   warps 2-3   one elected thread each issues the products of half the tile's vectors
+//               (A = G from TMEM, B from shared memory, M128 N32 K8 each) once the gather's
+//               mbarrier has completed, and commits to the mbarrier that frees the stage and
+//               the result buffer.  One thread issues a tcgen05.mma every 26 cycles at best
+//               (measured), and a step has 12 to 20 of them: three issuing threads keep the
+//               tensor pipe, not the issue slot, the bound.
+//   warps 4-7   one thread per (vector, kept row): fetches its index two to four steps ahead
+//               with cp.async (through column_info on the 64-k format), keeps P's one-hot
+//               entry current, and after the last step reads the accumulators (tcgen05.ld),
+//               transposes them through shared memory and stores C in 128-byte row pieces.
+// n_keep = 32 (nothing pruned) has the identity as its index list and multiplies A_window by
+// the B rows directly.  12:32 gathers 16 columns per vector of which 4 are zero (P has no
+// entry for them), and loads 16 rows of B per vector of which the last 4 meet those zeros.
 // Every wait is bounded; a wait that gives up raises the device status word.
 #include <cuda.h>
 
@@ -32,9 +48,7 @@
 
 namespace nmspmm {
 
-// Diagnostic build (-DNMSPMM_PROFILE_WAITS): the first gather warp and the MMA warp of every
-// CTA add up the cycles they spend in each phase.
-#ifdef NMSPMM_PROFILE_WAITS
+#ifdef NMSPMM_TF32_PROFILE
 __device__ unsigned long long g_tf32_profile[16];
 #define TF_DECL(...) long long __VA_ARGS__
 #define TF_T(name) const long long name = clock64()
@@ -47,82 +61,78 @@ __device__ unsigned long long g_tf32_profile[16];
 #define TF_OUT(i, v)
 #endif
 
-template <int WS, int KS_, int MODE, int QT_>
+template <int NKEEP, int KW_, int MODE, int QT_>
 struct Tf32Cfg {
     static constexpr int MS = 128, QT = QT_, NS = QT * 32;   // QT = 8: one CTA per SM; QT = 4: two
-    static constexpr int KS = KS_;
-    static constexpr int G = WS / 8;                       // MMAs (K = 8 each) per vector and window
-    static_assert(WS % 8 == 0, "kind::tf32 contracts 8 rows per instruction");
-    // 12:32 is staged as pairs of 32-k windows (24 kept rows, three MMAs): PAIR.
-    static constexpr bool PAIR = (MODE == kModeLow && KS == 64);
-    static constexpr int CH = (WS % 16 == 0) ? 16 : 8;     // TMEM columns per tcgen05.st
-    static constexpr int NCH = WS / CH;
-    static_assert(WS % CH == 0, "whole stores");
-    static constexpr int B_BYTES = QT * WS * 128;          // per vector WS rows of 128 bytes, swizzled; multiple of 1024
-    static constexpr int A_BYTES = KS * MS * 4;
-    static constexpr int D_BYTES = ((WS * (QT > 4 ? QT : 4) * 4 + 127) / 128) * 128;
-    static constexpr int CI_BYTES = (MODE == kModeHigh) ? QT * 256 : 0;
-    static constexpr int STAGE_BYTES = ((B_BYTES + A_BYTES + D_BYTES + CI_BYTES + 1023) / 1024) * 1024;
+    static constexpr int KW = KW_;                           // k per step
+    static constexpr int WS = NKEEP * (KW / 32);             // rows of B per step
+    static constexpr int WSP = (WS + 7) / 8 * 8;             // gathered columns per vector (K of the products)
+    static constexpr bool DIRECT = (NKEEP == 32);            // identity index list: no gather
+    static constexpr int G = WSP / 8;                        // product instructions per vector and step
+    static constexpr int NKS = KW / 8;                       // gather instructions per step
+    static constexpr int N1 = QT * WSP;                      // gathered columns per step
+    static_assert(DIRECT || N1 <= 128, "one builder thread per gathered column");
+    static_assert(MODE == kModeHigh || KW == 32, "only the 64-k format has merged windows");
+    static constexpr int A_BYTES = KW * 512;                 // [4 blocks of 32 rows of the tile][KW][32]
+    static constexpr int B_BYTES = QT * WSP * 128;           // [QT][WSP][32]
+    static constexpr int P_BYTES = DIRECT ? 0 : N1 * KW * 4; // [N1 / 32][KW][32]
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + P_BYTES;
+    static_assert(A_BYTES % 1024 == 0 && B_BYTES % 1024 == 0 && P_BYTES % 1024 == 0, "swizzle atoms stay aligned");
     static constexpr int CTAS_PER_SM = (QT == 8) ? 1 : 2;
-    static constexpr int ST0 = ((CTAS_PER_SM == 1 ? 216 : 108) * 1024) / STAGE_BYTES;
-    static constexpr int STAGES = ST0 >= 4 ? 4 : 2;        // even: a stage always serves the same group of gather warps
-    static constexpr int TMEM_COLS = 512 / CTAS_PER_SM;    // each resident CTA allocates its share
-    static constexpr int BUF_COLS = QT * WS;               // one A buffer: every vector of one window
-    static constexpr int NBUF0 = (TMEM_COLS - NS) / BUF_COLS;
-    static constexpr int NBUF = NBUF0 > 4 ? 4 : NBUF0;     // ring of A buffers beside the accumulators
-    static_assert(NBUF >= 1, "no room for an A buffer beside the accumulators");
-    static constexpr int GATHER_WARPS = 16;
-    // Groups of gather warps that take the windows in turn.  A warp's waits on one mbarrier
-    // must follow one another phase by phase (a waiter two phases ahead would see the
-    // parity it expects too early), so every A buffer and every stage has to stay with one
-    // group: two groups only when both ring depths are even.
-    static constexpr int GROUPS = (NBUF % 2 == 0 && STAGES % 2 == 0) ? 2 : 1;
-    static constexpr int GROUP_WARPS = GATHER_WARPS / GROUPS;
-    static constexpr int VSTEP = GROUP_WARPS / 4;          // vectors a group gathers at a time
-    static constexpr int VPW = QT / VSTEP;                 // vectors each gather warp carries per window
-    static_assert(GROUP_WARPS % 4 == 0 && QT % VSTEP == 0, "four warps (TMEM lane quadrants) per vector");
-    static_assert(VPW % GROUPS == 0, "the epilogue shares each warp's vectors out among the groups");
-    static constexpr int THREADS = (2 + GATHER_WARPS) * 32;
-    static constexpr int NBARS = 2 * STAGES + 2 * NBUF + 1;
-    static constexpr int CTRL_BYTES = ((NBARS * 8 + 16 + 127) / 128) * 128;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + CTRL_BYTES + 1024;   // + alignment slack
-    static constexpr int ACOL0 = NS;                       // first A-buffer column
-    static constexpr bool HALF = false;
+    static constexpr int TMEM_COLS = 512 / CTAS_PER_SM;      // each resident CTA allocates its share
+    static constexpr int PD = 2;                             // index prefetch distance, in steps, per look-up
+    static constexpr int RING = 4 * PD;                      // slots of the per-thread index rings
+    static constexpr int BUILDERS = 128;
+    static constexpr int PRODUCT_WARPS = 2;
+    static constexpr int THREADS = (2 + PRODUCT_WARPS) * 32 + BUILDERS;
+    static constexpr int AUX_BYTES = (2 * RING + 8) * BUILDERS * 4;    // index rings + previous one-hot per stage (<= 8 stages)
+    static constexpr int CTRL_BYTES = 256;
+    static constexpr int SMEM_LIMIT = (CTAS_PER_SM == 1 ? 227 : 113) * 1024;
+    static constexpr int ST0 = (SMEM_LIMIT - 1024 - AUX_BYTES - CTRL_BYTES) / STAGE_BYTES;
+    static constexpr int STAGES = ST0 > 6 ? 6 : ST0;
+    static_assert(STAGES >= 2, "at least two stages");
+    // Ring of gather results beside the accumulators.  The gather of step t waits for the
+    // products of step t - NBUF through that step's stage barrier, whose phase must still be
+    // the current one: NBUF < STAGES.
+    static constexpr int NBUF0 = DIRECT ? 1 : (TMEM_COLS - NS) / N1;
+    static constexpr int NBUF1 = NBUF0 > 3 ? 3 : NBUF0;
+    static constexpr int NBUF = NBUF1 >= STAGES ? STAGES - 1 : NBUF1;
+    static_assert(NBUF >= 1, "no room for a gather result beside the accumulators");
+    static constexpr int EPI_BYTES = 4 * 32 * 144;           // four warps' 32 x 32 transposition patches, rows 144 bytes apart
+    static_assert(EPI_BYTES <= STAGES * STAGE_BYTES, "the epilogue reuses the stage ring");
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + AUX_BYTES + CTRL_BYTES + 1024;   // + alignment slack
+    static constexpr int ACOL0 = NS;                         // first gather-result column
 };
 
-// Whole warp: each thread stores CH (8 or 16) consecutive 32-bit columns of its own lane.
-template <int CH>
-__device__ __forceinline__ void tmem_st_chunk(uint32_t taddr, const uint32_t (&v)[CH])
+// Byte offset of P[k][n] (n = gathered column) inside a stage's P region.
+template <int KW>
+__device__ __forceinline__ uint32_t p_offset(int n, int k)
 {
-    if constexpr (CH == 8) {
-        tmem_st_x8(taddr, v);
-    } else {
-        static_assert(CH == 16, "8 or 16 columns per store");
-        asm volatile(
-            "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-            "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-            ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
-              "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
-            : "memory");
-    }
+    const int nb = n >> 5, c = n & 31;
+    return static_cast<uint32_t>(nb * (KW * 128) + k * 128 + ((((c >> 3) ^ (k & 3)) << 5) | ((c & 7) << 2)));
 }
 
-template <int WS, int KS_, int MODE, int QT_>
-__global__ void __launch_bounds__((Tf32Cfg<WS, KS_, MODE, QT_>::THREADS), (Tf32Cfg<WS, KS_, MODE, QT_>::CTAS_PER_SM))
+template <int NKEEP, int KW_, int MODE, int QT_>
+__global__ void __launch_bounds__((Tf32Cfg<NKEEP, KW_, MODE, QT_>::THREADS), (Tf32Cfg<NKEEP, KW_, MODE, QT_>::CTAS_PER_SM))
 nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    const GemmOutputs outs)
+                    const GemmOutputs outs, const int a_blocked)
 {
-    using Cfg = Tf32Cfg<WS, KS_, MODE, QT_>;
-    constexpr int MS = Cfg::MS, NS = Cfg::NS, QT = Cfg::QT, KS = Cfg::KS, G = Cfg::G, STAGES = Cfg::STAGES, NBUF = Cfg::NBUF;
-    constexpr int CH = Cfg::CH, NCH = Cfg::NCH, VPW = Cfg::VPW;
+    using Cfg = Tf32Cfg<NKEEP, KW_, MODE, QT_>;
+    constexpr int MS = Cfg::MS, NS = Cfg::NS, QT = Cfg::QT, KW = Cfg::KW, WS = Cfg::WS, WSP = Cfg::WSP;
+    constexpr int STAGES = Cfg::STAGES, NBUF = Cfg::NBUF, RING = Cfg::RING, PD = Cfg::PD;
+    constexpr bool DIRECT = Cfg::DIRECT;
+    constexpr int FIRST_BUILDER = 2 + Cfg::PRODUCT_WARPS;
 
     extern __shared__ unsigned char smem_raw[];
     const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;          // swizzle atoms want 1024-byte alignment
-    const uint32_t bars = ring + STAGES * Cfg::STAGE_BYTES;
+    const uint32_t idx_ring = ring + STAGES * Cfg::STAGE_BYTES;           // [RING][128] raw index (rank on the 64-k format)
+    const uint32_t k_ring = idx_ring + RING * 512;                        // [RING][128] k after the column_info look-up
+    const uint32_t prev_k = k_ring + RING * 512;                          // [STAGES][128] one-hot entry now set in the stage
+    const uint32_t bars = ring + STAGES * Cfg::STAGE_BYTES + Cfg::AUX_BYTES;
     const uint32_t bar_full = bars, bar_empty = bars + STAGES * 8;
-    const uint32_t bar_aready = bar_empty + STAGES * 8, bar_afree = bar_aready + NBUF * 8;
-    const uint32_t bar_acc = bar_afree + NBUF * 8;
+    const uint32_t bar_gdone = bar_empty + STAGES * 8, bar_acc = bar_gdone + 3 * 8;
     const uint32_t tmem_word = bar_acc + 8, abort_word = tmem_word + 4;
+    static_assert((2 * 6 + 3 + 1) * 8 + 8 <= Cfg::CTRL_BYTES, "control block");
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // The first n_dp CTAs take one whole tile each.  The remaining tiles (the partial last
@@ -136,29 +146,29 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
     const int tile = sliced ? n_dp + slot / n_slices : static_cast<int>(blockIdx.x);
     const int ty = tile / g.tiles_x, tx = tile - ty * g.tiles_x;
     const int bi = ty * MS, bj = tx * NS;
-    int win0, n_win;                                       // this CTA's k windows: win0 .. win0 + n_win - 1
+    int win0, n_win;                                       // this CTA's steps: win0 .. win0 + n_win - 1
     slice_range(g.sched.n_win, n_slices, sliced ? slot % n_slices : 0, win0, n_win);
     const int live_vecs = min(QT, (g.N - bj) / 32);        // vectors of the tile that exist
-    const int qs_shift = g.qs_shift, layout_shift = qs_shift + 5;
-    const int d_chunk = WS << qs_shift;
-    const uint32_t d_bytes = static_cast<uint32_t>(d_chunk) * 4u;
-    const int lb0 = bj >> layout_shift;
-    const int nlb = ((bj + live_vecs * 32 - 1) >> layout_shift) - lb0 + 1;
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(bar_full + s * 8, 1);
-            mbar_init(bar_empty + s * 8, Cfg::GROUP_WARPS + 1);           // the window's gather warps + the MMA commit
+            mbar_init(bar_full + s * 8, DIRECT ? 1 : 1 + Cfg::BUILDERS / 32);   // the TMA bytes + the builder warps
+            mbar_init(bar_empty + s * 8, DIRECT ? 1 : Cfg::PRODUCT_WARPS);      // the commits behind the step's products
         }
-        for (int b = 0; b < NBUF; ++b) {
-            mbar_init(bar_aready + b * 8, Cfg::GROUP_WARPS);
-            mbar_init(bar_afree + b * 8, 1);                              // the MMA commit
-        }
-        mbar_init(bar_acc, 1);
+        for (int b = 0; b < 3; ++b) mbar_init(bar_gdone + b * 8, 1);
+        mbar_init(bar_acc, DIRECT ? 1 : Cfg::PRODUCT_WARPS);
         sts_volatile_s32(abort_word, 0);
         mbar_init_fence();
     }
     if (warp == 1) tmem_alloc(tmem_word, Cfg::TMEM_COLS);
+    if (!DIRECT) {
+        // P starts as all zeros; 12:32 also wants the never-set columns of every vector zero
+        const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s = 0; s < STAGES; ++s)
+            for (int o = tid * 16; o < Cfg::P_BYTES; o += Cfg::THREADS * 16)
+                sts_f4(ring + s * Cfg::STAGE_BYTES + Cfg::A_BYTES + Cfg::B_BYTES + o, z);
+        fence_proxy_async();
+    }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -166,184 +176,240 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
+        TF_DECL(p_empty = 0);
+        TF_T(p_start);
         for (int it = 0; it < n_win; ++it) {
             const int s = it % STAGES;
             if (it >= STAGES) {
+                TF_T(t0);
                 const bool ok = mbar_wait_bounded(bar_empty + s * 8, ((it / STAGES) - 1) & 1, abort_word);
+                TF_ADD(p_empty, t0);
                 if (!__all_sync(0xffffffffu, ok)) {
                     if (lane == 0) atomicMax(g.status, kDevTimeoutEmpty);
                     break;
                 }
             }
             const uint32_t st = ring + s * Cfg::STAGE_BYTES, full = bar_full + s * 8;
-            const uint32_t as = st + Cfg::B_BYTES, ds = as + Cfg::A_BYTES;
             if (elect_one()) {
-                mbar_arrive_expect_tx(full, Cfg::A_BYTES + live_vecs * (WS * 128) +
-                                                nlb * (d_bytes + (MODE == kModeHigh ? 256u : 0u)));
-                for (int b = 0; b < nlb; ++b) {            // the indices first: the gather starts from them
-                    const int* src = g.D + ((static_cast<size_t>(lb0 + b) * g.W) << qs_shift) + static_cast<size_t>(win0 + it) * d_chunk;
-                    bulk_g2s(ds + b * d_bytes, src, d_bytes, full);
-                    if (MODE == kModeHigh) {
-                        const int* ci = g.cinfo + (static_cast<size_t>(lb0 + b) * g.sched.n_win + win0 + it) * 64;
-                        bulk_g2s(ds + Cfg::D_BYTES + b * 256, ci, 256, full);
-                    }
+                mbar_arrive_expect_tx(full, Cfg::A_BYTES + Cfg::B_BYTES);
+                if (a_blocked) {
+                    tma_load_3d(st, &map_a, 0, (win0 + it) * KW, bi >> 5, full);
+                } else {                                   // rows not a multiple of 32: four boxes of 32 rows, the ragged one zero-filled
+                    for (int mb = 0; mb < 4; ++mb) tma_load_2d(st + mb * (KW * 128), &map_a, bi + mb * 32, (win0 + it) * KW, full);
                 }
-                tma_load_2d(as, &map_a, bi, (win0 + it) * KS, full);
-                for (int v = 0; v < live_vecs; ++v) tma_load_2d(st + v * (WS * 128), &map_b, bj + v * 32, (win0 + it) * WS, full);
+                tma_load_3d(st + Cfg::A_BYTES, &map_b, 0, (win0 + it) * WS, bj >> 5, full);
             }
             __syncwarp();
         }
+#ifdef NMSPMM_TF32_PROFILE
+        if (lane == 0) { TF_OUT(0, p_empty); TF_OUT(1, clock64() - p_start); }
+#endif
     } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
-        constexpr uint32_t idesc = umma_idesc_tf32(128, 32);
+        // ------------------------------------------------------------------ gather issuer
+        constexpr uint32_t idesc_gather = umma_idesc_tf32(128, DIRECT ? 32 : Cfg::N1, true);
+        const uint32_t idesc_direct = umma_idesc_tf32(128, live_vecs * 32, true);
         bool alive = true;
-        TF_DECL(m_full = 0, m_ready = 0, m_issue = 0);
+        TF_DECL(m_full = 0, m_free = 0, m_issue = 0);
         TF_T(m_start);
-        for (int it = 0; it < n_win; ++it) {
-            const int s = it % STAGES, b = it % NBUF;
+        for (int t = 0; t < n_win; ++t) {
+            const int s = t % STAGES;
             TF_T(t0);
-            bool ok = mbar_wait_bounded(bar_full + s * 8, (it / STAGES) & 1, abort_word);
+            bool ok = mbar_wait_bounded(bar_full + s * 8, (t / STAGES) & 1, abort_word);
             TF_ADD(m_full, t0);
             TF_T(t1);
-            ok = ok && mbar_spin_bounded(bar_aready + b * 8, (it / NBUF) & 1, abort_word);
+            if (!DIRECT && t >= NBUF) {                    // the result buffer is free once the products of step t - NBUF are done
+                const int u = t - NBUF;
+                ok = ok && mbar_wait_bounded(bar_empty + (u % STAGES) * 8, (u / STAGES) & 1, abort_word);
+            }
+            TF_ADD(m_free, t1);
             if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
-            TF_ADD(m_ready, t1);
             TF_T(t2);
             tc_fence_after_sync();
             if (elect_one()) {
                 const uint32_t st = ring + s * Cfg::STAGE_BYTES;
-                const uint32_t abuf = tmem_addr(tmem, 0, Cfg::ACOL0 + b * Cfg::BUF_COLS);
-                for (int v = 0; v < live_vecs; ++v) {
+                if (DIRECT) {
 #pragma unroll
-                    for (int gi = 0; gi < G; ++gi)
-                        umma_tf32_ts(tmem_addr(tmem, 0, v * 32), abuf + v * WS + gi * 8,
-                                     umma_desc_mn_tf32(st + v * (WS * 128) + gi * 1024), idesc, (it | gi) != 0);
+                    for (int ks = 0; ks < Cfg::NKS; ++ks)
+                        umma_tf32_ss(tmem_addr(tmem, 0, 0), umma_desc_mn_tf32(st + ks * 1024, KW * 128, 512),
+                                     umma_desc_mn_tf32(st + Cfg::A_BYTES + ks * 1024, WSP * 128, 512), idesc_direct,
+                                     (t | ks) != 0);
+                    tc_commit(bar_empty + s * 8);
+                } else {
+                    const uint32_t gbuf = tmem_addr(tmem, 0, Cfg::ACOL0 + (t % NBUF) * Cfg::N1);
+#pragma unroll
+                    for (int ks = 0; ks < Cfg::NKS; ++ks)
+                        umma_tf32_ss(gbuf, umma_desc_mn_tf32(st + ks * 1024, KW * 128, 512),
+                                     umma_desc_mn_tf32(st + Cfg::A_BYTES + Cfg::B_BYTES + ks * 1024, KW * 128, 512),
+                                     idesc_gather, ks != 0);
+                    tc_commit(bar_gdone + (t % NBUF) * 8);
                 }
-                tc_commit(bar_afree + b * 8);              // the A buffer is free once these MMAs have read it
-                tc_commit(bar_empty + s * 8);              // and so are the window's B blocks
             }
             __syncwarp();
             TF_ADD(m_issue, t2);
         }
-#ifdef NMSPMM_PROFILE_WAITS
-        if (lane == 0) { TF_OUT(7, m_full); TF_OUT(8, m_ready); TF_OUT(9, m_issue); TF_OUT(10, clock64() - m_start); }
+#ifdef NMSPMM_TF32_PROFILE
+        if (lane == 0) {
+            TF_OUT(2, m_full); TF_OUT(3, m_free); TF_OUT(4, m_issue); TF_OUT(5, clock64() - m_start); TF_OUT(8, 1); TF_OUT(9, n_win);
+        }
 #endif
         if (!alive && lane == 0) atomicMax(g.status, kDevTimeoutMma);
-        if (elect_one()) tc_commit(bar_acc);               // every MMA has completed: accumulators are final
-        __syncwarp();
-    } else {
-        // ------------------------------------------------------------------ gather warps
-        const int gw = warp - 2;                           // 0..15
-        const int quad = warp & 3;                         // TMEM lane quadrant this warp may touch
-        const int row = quad * 32 + lane;                  // row of the tile this thread carries
-        const int grp = gw / Cfg::GROUP_WARPS;             // its windows: grp, grp + GROUPS, ...
-        const int v0 = (gw % Cfg::GROUP_WARPS) >> 2;       // its vectors: v0, v0 + VSTEP, ...
-        constexpr int VSTEP = Cfg::VSTEP;
-        // where lane p finds index p of vector v0 + 4 i within the staged index block
-        uint32_t d_rel[VPW], ci_rel[VPW];
-#pragma unroll
-        for (int i = 0; i < VPW; ++i) {
-            const int q = (bj >> 5) + v0 + VSTEP * i;
-            const int lb = (q >> qs_shift) - lb0;
-            d_rel[i] = static_cast<uint32_t>(lb * d_chunk + (lane << qs_shift) + (q & ((1 << qs_shift) - 1))) * 4u;
-            ci_rel[i] = static_cast<uint32_t>(lb * 256);
+        if (DIRECT) {
+            if (elect_one()) tc_commit(bar_acc);           // every MMA has completed: accumulators are final
+            __syncwarp();
         }
-        bool alive = true;
-        TF_DECL(g_full = 0, g_res = 0, g_free = 0, g_move = 0, g_done = 0);
-        TF_T(g_start);
-        for (int it = grp; it < n_win; it += Cfg::GROUPS) {
-            const int s = it % STAGES, b = it % NBUF;
-            TF_T(t0);
-            bool ok = mbar_wait_bounded(bar_full + s * 8, (it / STAGES) & 1, abort_word);
-            if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
-            TF_ADD(g_full, t0);
-            TF_T(t1);
-            const uint32_t st = ring + s * Cfg::STAGE_BYTES;
-            const uint32_t as = st + Cfg::B_BYTES + row * 4, ds = st + Cfg::B_BYTES + Cfg::A_BYTES, cs = ds + Cfg::D_BYTES;
-            // lane p resolves index p of each of the warp's vectors to a byte offset into As
-            uint32_t off[VPW];
-#pragma unroll
-            for (int i = 0; i < VPW; ++i) {
-                int k = 0;
-                if (lane < WS && v0 + VSTEP * i < live_vecs) {
-                    k = lds_s32(ds + d_rel[i]);
-                    if (MODE == kModeHigh) k = lds_s32(cs + ci_rel[i] + k * 4);
-                    if (Cfg::PAIR && lane >= WS / 2) k += 32;      // second window of the pair
-                }
-                off[i] = static_cast<uint32_t>(k) * (MS * 4);
-            }
-            TF_ADD(g_res, t1);
-            TF_T(t2);
-            if (it >= NBUF) {
-                ok = mbar_wait_bounded(bar_afree + b * 8, ((it / NBUF) - 1) & 1, abort_word);
+    } else if (warp < FIRST_BUILDER) {
+        // ------------------------------------------------------------------ product issuers
+        if (!DIRECT) {
+            constexpr uint32_t idesc_product = umma_idesc_tf32(128, 32, false);
+            constexpr int VPI = QT / Cfg::PRODUCT_WARPS;   // vectors per issuer
+            const int v_begin = (warp - 2) * VPI, v_end = min(v_begin + VPI, live_vecs);
+            bool alive = true;
+            TF_DECL(c_gdone = 0, c_issue = 0);
+            TF_T(c_start);
+            for (int u = 0; u < n_win; ++u) {
+                const int s = u % STAGES, b = u % NBUF;
+                TF_T(t0);
+                // the step's B rows have landed (their barrier completed before the gather was issued)
+                bool ok = mbar_wait_bounded(bar_full + s * 8, (u / STAGES) & 1, abort_word);
+                ok = ok && mbar_spin_bounded(bar_gdone + b * 8, (u / NBUF) & 1, abort_word);
+                TF_ADD(c_gdone, t0);
                 if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+                TF_T(t1);
                 tc_fence_after_sync();
-            }
-            TF_ADD(g_free, t2);
-            TF_T(t3);
+                if (elect_one()) {
+                    if (v_begin < v_end) {
+                        const uint32_t bs = ring + s * Cfg::STAGE_BYTES + Cfg::A_BYTES;
+                        const uint32_t gbuf = tmem_addr(tmem, 0, Cfg::ACOL0 + b * Cfg::N1);
+                        for (int v = v_begin; v < v_end; ++v) {
 #pragma unroll
-            for (int i = 0; i < VPW; ++i) {
-                const int v = v0 + VSTEP * i;
-                if (v < live_vecs) {                       // warp-uniform
-#pragma unroll
-                    for (int c = 0; c < NCH; ++c) {
-                        uint32_t a[CH];
-#pragma unroll
-                        for (int j = 0; j < CH; ++j) a[j] = lds_u32(as + __shfl_sync(0xffffffffu, off[i], c * CH + j));
-                        tmem_st_chunk<CH>(tmem_addr(tmem, quad * 32, Cfg::ACOL0 + b * Cfg::BUF_COLS + v * WS + c * CH), a);
+                            for (int gi = 0; gi < Cfg::G; ++gi)
+                                umma_tf32_ts(tmem_addr(tmem, 0, v * 32), gbuf + v * WSP + gi * 8,
+                                             umma_desc_mn_tf32(bs + v * (WSP * 128) + gi * 1024), idesc_product, (u | gi) != 0);
+                        }
+                        tc_commit(bar_empty + s * 8);      // this half of the step's products has read the stage and the gather result
+                    } else {
+                        mbar_arrive(bar_empty + s * 8);    // no vector of this half exists; the gather itself has completed
                     }
                 }
+                __syncwarp();
+                TF_ADD(c_issue, t1);
             }
-            TF_ADD(g_move, t3);
-            TF_T(t4);
-            tmem_wait_st();
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(bar_aready + b * 8);
-                mbar_arrive(bar_empty + s * 8);            // this warp has finished reading As of the stage
-            }
-            TF_ADD(g_done, t4);
-        }
-#ifdef NMSPMM_PROFILE_WAITS
-        if (gw == 0 && lane == 0) {
-            TF_OUT(0, g_full); TF_OUT(1, g_res); TF_OUT(2, g_free); TF_OUT(3, g_move); TF_OUT(4, g_done);
-            TF_OUT(5, clock64() - g_start); TF_OUT(6, 1);
-        }
+#ifdef NMSPMM_TF32_PROFILE
+            if (lane == 0 && warp == 2) { TF_OUT(6, c_gdone); TF_OUT(7, c_issue); TF_OUT(15, clock64() - c_start); }
 #endif
+            if (!alive && lane == 0) atomicMax(g.status, kDevTimeoutMma);
+            if (elect_one()) {
+                if (v_begin < v_end) tc_commit(bar_acc); else mbar_arrive(bar_acc);
+            }
+            __syncwarp();
+        }
+    } else {
+        // ------------------------------------------------------------------ one-hot builders
+        const int e = tid - FIRST_BUILDER * 32;            // gathered column this thread keeps
+        const int quad = warp & 3;                         // TMEM lane quadrant this warp may touch
+        bool alive = true;
+        if (!DIRECT) {
+            const int v = e / WSP, j = e % WSP;
+            const bool has = e < Cfg::N1 && j < WS && v < live_vecs;
+            const int q = (bj >> 5) + v, qs_shift = g.qs_shift;
+            const int* dptr = g.D + ((static_cast<size_t>(q >> qs_shift) * g.W) << qs_shift) + (q & ((1 << qs_shift) - 1)) +
+                              (static_cast<size_t>(j) << qs_shift);
+            const int n_merged = (KW == 64) ? g.sched.n_win : (g.sched.n_win >> 1);
+            const int* ciptr = (MODE == kModeHigh) ? g.cinfo + static_cast<size_t>(q >> qs_shift) * n_merged * 64 : nullptr;
+            const uint32_t my_idx = idx_ring + e * 4, my_k = k_ring + e * 4, my_prev = prev_k + e * 4;
+            for (int s = 0; s < STAGES; ++s) sts_s32(my_prev + s * 512, -1);
+            TF_DECL(b_cp = 0, b_empty = 0);
+            TF_T(b_start);
+            for (int i = -2 * PD; i < n_win; ++i) {
+                TF_T(t0);
+                cp_async_wait<PD - 1>();                   // the copies issued PD iterations ago and earlier have landed
+                TF_ADD(b_cp, t0);
+                int k = 0;
+                if (has && i >= 0) {
+                    k = lds_s32((MODE == kModeHigh ? my_k : my_idx) + (i & (RING - 1)) * 512);
+                    if (MODE == kModeHigh && KW == 32) k -= ((win0 + i) & 1) * 32;
+                }
+                if (has) {
+                    const int i2 = i + 2 * PD, i1 = i + PD;
+                    if (i2 < n_win)
+                        cp_async_4(my_idx + (i2 & (RING - 1)) * 512, dptr + ((static_cast<size_t>(win0 + i2) * WS) << qs_shift));
+                    if (MODE == kModeHigh && i1 >= 0 && i1 < n_win) {
+                        const int rank = lds_s32(my_idx + (i1 & (RING - 1)) * 512);
+                        const int m = (KW == 64) ? (win0 + i1) : ((win0 + i1) >> 1);
+                        cp_async_4(my_k + (i1 & (RING - 1)) * 512, ciptr + static_cast<size_t>(m) * 64 + rank);
+                    }
+                }
+                cp_async_commit();
+                if (i < 0) continue;
+                const int s = i % STAGES;
+                if (i >= STAGES) {
+                    TF_T(t1);
+                    const bool ok = mbar_wait_bounded(bar_empty + s * 8, ((i / STAGES) - 1) & 1, abort_word);
+                    TF_ADD(b_empty, t1);
+                    if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+                }
+                if (has) {
+                    const uint32_t ps = ring + s * Cfg::STAGE_BYTES + Cfg::A_BYTES + Cfg::B_BYTES;
+                    const int old = lds_s32(my_prev + s * 512);
+                    if (old >= 0) sts_f32(ps + p_offset<KW>(e, old), 0.f);
+                    sts_f32(ps + p_offset<KW>(e, k), 1.f);
+                    sts_s32(my_prev + s * 512, k);
+                }
+                fence_proxy_async();                       // the tensor core reads P through the asynchronous proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_full + s * 8);
+            }
+            cp_async_wait<0>();
+#ifdef NMSPMM_TF32_PROFILE
+            if (e == 0) { TF_OUT(10, b_cp); TF_OUT(11, b_empty); TF_OUT(12, clock64() - b_start); }
+#endif
+        }
         // ------------------------------------------------------------------ epilogue
+        TF_T(e_start);
         bool ok = alive && mbar_wait_bounded(bar_acc, 0, abort_word);
         ok = __all_sync(0xffffffffu, ok);
+        TF_T(e_go);
         if (ok) {
             tc_fence_after_sync();
-            const int r = bi + row;
+            // every MMA has completed, so every TMA copy has landed and been read: the
+            // stage ring is free and serves as the transposition patches
+            const uint32_t patch = ring + (warp - FIRST_BUILDER) * (32 * 144);
+            const int r_sub = lane >> 3, c4 = (lane & 7) * 4;     // store phase: 4 rows x 8 float4 per instruction
+            float* const out0 = sliced ? g.partial + static_cast<size_t>(slot) * MS * NS : nullptr;
 #pragma unroll 1
-            for (int i = grp; i < VPW; i += Cfg::GROUPS) {  // the groups share the warp's vectors out
-                const int col = (v0 + VSTEP * i) * 32;
-                if (col >= live_vecs * 32) break;
-                uint32_t v[32];
-                tmem_ld_x32(tmem_addr(tmem, quad * 32, col), v);
+            for (int v = 0; v < live_vecs; ++v) {
+                uint32_t acc[32];
+                tmem_ld_x32(tmem_addr(tmem, quad * 32, v * 32), acc);
                 tmem_wait_ld();
-                if (sliced) {
-                    float4* dst = reinterpret_cast<float4*>(g.partial + (static_cast<size_t>(slot) * MS + row) * NS + col);
+                __syncwarp();                              // the previous vector's reads of the patch are over
 #pragma unroll
-                    for (int x = 0; x < 8; ++x)
-                        dst[x] = make_float4(__uint_as_float(v[4 * x]), __uint_as_float(v[4 * x + 1]),
-                                             __uint_as_float(v[4 * x + 2]), __uint_as_float(v[4 * x + 3]));
-                } else if (r < g.M) {
-                    const size_t at = static_cast<size_t>(r) * outs.ldc + outs.col0 + bj + col;
-                    for (int o = 0; o < outs.n_out; ++o) {   // every output (peers' copies of C when gathering)
-                        float4* dst = reinterpret_cast<float4*>(output_of(g, outs, o) + at);
+                for (int x = 0; x < 8; ++x)
+                    sts_f4(patch + lane * 144 + x * 16,
+                           make_float4(__uint_as_float(acc[4 * x]), __uint_as_float(acc[4 * x + 1]),
+                                       __uint_as_float(acc[4 * x + 2]), __uint_as_float(acc[4 * x + 3])));
+                __syncwarp();
+#ifndef NMSPMM_TF32_NOSTORE
 #pragma unroll
-                        for (int x = 0; x < 8; ++x)
-                            dst[x] = make_float4(__uint_as_float(v[4 * x]), __uint_as_float(v[4 * x + 1]),
-                                                 __uint_as_float(v[4 * x + 2]), __uint_as_float(v[4 * x + 3]));
+                for (int rr = 0; rr < 32; rr += 4) {
+                    const int row = quad * 32 + rr + r_sub;
+                    const float4 val = lds_f4(patch + (rr + r_sub) * 144 + c4 * 4);
+                    if (sliced) {
+                        *reinterpret_cast<float4*>(out0 + static_cast<size_t>(row) * NS + v * 32 + c4) = val;
+                    } else if (bi + row < g.M) {
+                        const size_t at = static_cast<size_t>(bi + row) * outs.ldc + outs.col0 + bj + v * 32 + c4;
+                        *reinterpret_cast<float4*>(g.C + at) = val;
+                        for (int o = 1; o < outs.n_out; ++o)     // peers' copies of C when gathering
+                            *reinterpret_cast<float4*>(outs.C_more[o - 1] + at) = val;
                     }
                 }
+#endif
             }
         } else if (lane == 0) {
             atomicMax(g.status, kDevTimeoutMma);
         }
+#ifdef NMSPMM_TF32_PROFILE
+        if (e == 0) { TF_OUT(13, e_go - e_start); TF_OUT(14, clock64() - e_go); }
+#endif
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -353,11 +419,11 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
     }
 }
 
-template <int WS, int KS, int MODE, int QT>
+template <int NKEEP, int KW, int MODE, int QT>
 static cudaError_t launch_tf32(const GemmArgs& a, const GemmOutputs& outs, int tiles, cudaStream_t st)
 {
-    using Cfg = Tf32Cfg<WS, KS, MODE, QT>;
-    auto kernel = nm_gemm_tf32_kernel<WS, KS, MODE, QT>;
+    using Cfg = Tf32Cfg<NKEEP, KW, MODE, QT>;
+    auto kernel = nm_gemm_tf32_kernel<NKEEP, KW, MODE, QT>;
     static bool configured[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -368,29 +434,32 @@ static cudaError_t launch_tf32(const GemmArgs& a, const GemmOutputs& outs, int t
         configured[dev] = true;
     }
     CUtensorMap map_a, map_b;
-    e = encode_tensor_map_2d(&map_a, a.A, a.M, a.sched.n_win * KS, Cfg::MS, KS, 0);
+    const int K = a.sched.n_win * KW;
+    const int a_blocked = (a.M % 32 == 0) ? 1 : 0;
+    e = a_blocked ? encode_tensor_map_blocks32(&map_a, a.A, a.M, K, KW, 4)
+                  : encode_tensor_map_2d(&map_a, a.A, a.M, K, 32, KW, 1);
     if (e != cudaSuccess) return e;
-    e = encode_tensor_map_2d(&map_b, a.B, a.N, a.W, 32, WS, 1);      // 32-byte chunks swizzled in 128-byte rows
+    e = encode_tensor_map_blocks32(&map_b, a.B, a.N, a.W, Cfg::WSP, QT);
     if (e != cudaSuccess) return e;
-    kernel<<<tiles, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(a, map_a, map_b, outs);
+    kernel<<<tiles, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(a, map_a, map_b, outs, a_blocked);
     return cudaGetLastError();
 }
 
-#define NMSPMM_TF32_VARIANT(NKEEP, WS, KS, MODE, QT)                                                        \
-    { NKEEP, WS, KS, MODE, QT * 32, Tf32Cfg<WS, KS, MODE, QT>::SMEM_BYTES, Tf32Cfg<WS, KS, MODE, QT>::STAGES, \
-      &launch_tf32<WS, KS, MODE, QT> }
+#define NMSPMM_TF32_VARIANT(NKEEP, KW, MODE, QT)                                                                   \
+    { NKEEP, Tf32Cfg<NKEEP, KW, MODE, QT>::WS, KW, MODE, QT * 32, Tf32Cfg<NKEEP, KW, MODE, QT>::SMEM_BYTES,        \
+      Tf32Cfg<NKEEP, KW, MODE, QT>::STAGES, Tf32Cfg<NKEEP, KW, MODE, QT>::THREADS, &launch_tf32<NKEEP, KW, MODE, QT> }
 
 extern const Tf32Variant kTf32Variants[] = {
-    NMSPMM_TF32_VARIANT(32, 32, 32, kModeLow, 8),  NMSPMM_TF32_VARIANT(32, 32, 32, kModeLow, 4),
-    NMSPMM_TF32_VARIANT(16, 16, 32, kModeLow, 8),  NMSPMM_TF32_VARIANT(16, 16, 32, kModeLow, 4),
-    NMSPMM_TF32_VARIANT(12, 24, 64, kModeLow, 8),  NMSPMM_TF32_VARIANT(12, 24, 64, kModeLow, 4),
-    NMSPMM_TF32_VARIANT(8, 8, 32, kModeLow, 8),    NMSPMM_TF32_VARIANT(8, 8, 32, kModeLow, 4),
-    NMSPMM_TF32_VARIANT(8, 16, 64, kModeHigh, 8),  NMSPMM_TF32_VARIANT(8, 16, 64, kModeHigh, 4),
-    NMSPMM_TF32_VARIANT(4, 8, 64, kModeHigh, 8),   NMSPMM_TF32_VARIANT(4, 8, 64, kModeHigh, 4),
+    NMSPMM_TF32_VARIANT(32, 32, kModeLow, 8),  NMSPMM_TF32_VARIANT(32, 32, kModeLow, 4),
+    NMSPMM_TF32_VARIANT(16, 32, kModeLow, 8),  NMSPMM_TF32_VARIANT(16, 32, kModeLow, 4),
+    NMSPMM_TF32_VARIANT(12, 32, kModeLow, 8),  NMSPMM_TF32_VARIANT(12, 32, kModeLow, 4),
+    NMSPMM_TF32_VARIANT(8, 32, kModeLow, 8),   NMSPMM_TF32_VARIANT(8, 32, kModeLow, 4),
+    NMSPMM_TF32_VARIANT(8, 32, kModeHigh, 8),  NMSPMM_TF32_VARIANT(8, 32, kModeHigh, 4),
+    NMSPMM_TF32_VARIANT(4, 64, kModeHigh, 8),  NMSPMM_TF32_VARIANT(4, 64, kModeHigh, 4),
 };
 extern const int kTf32VariantCount = sizeof(kTf32Variants) / sizeof(kTf32Variants[0]);
 
-#ifdef NMSPMM_PROFILE_WAITS
+#ifdef NMSPMM_TF32_PROFILE
 // Diagnostic build only: reads and clears the phase counters.
 extern "C" int nmspmm_debug_tf32_profile(unsigned long long* out16)
 {

@@ -33,13 +33,18 @@ const FfmaVariant* find_ffma_variant(int tile_id, int n_keep, int mode);
 cudaError_t encode_tensor_map_2d(CUtensorMap* map, const float* base, int cols, int rows, int box_cols, int box_rows,
                                  int swizzle128 = 0);
 
+// Row-major [rows][cols] float tensor as blocks of 32 columns (cols % 32 == 0): a box of
+// box_blocks blocks x box_rows rows lands block after block, each [box_rows][32] swizzled like
+// encode_tensor_map_2d's swizzle128 form.
+cudaError_t encode_tensor_map_blocks32(CUtensorMap* map, const float* base, int cols, int rows, int box_rows, int box_blocks);
+
 // One compiled TF32 tensor-core kernel variant (tile 128 x ns).
 struct Tf32Variant {
     int n_keep;         // kept rows per 32-k window
-    int ws, ks;         // rows of B / of A per staged window
+    int ws, ks;         // rows of B / of A per step
     int mode;
     int ns;             // tile columns: 256 (one CTA per SM) or 128 (two)
-    int smem_bytes, stages;
+    int smem_bytes, stages, threads;
     cudaError_t (*launch)(const GemmArgs&, const GemmOutputs&, int tiles, cudaStream_t st);
 };
 extern const Tf32Variant kTf32Variants[];

@@ -58,30 +58,31 @@ __device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t (&v)[32])
         : "memory");
 }
 
-// Shared-memory descriptor of an MN-major TF32 operand block of 32 values (128 bytes)
-// along N by 8 rows along K, rows 128 bytes apart, at a 512-byte-aligned address.  MN-major
-// 32-bit operands have one legal layout: 128-byte rows whose 32-byte chunks are XOR-ed with
-// (row % 4) -- layout type 1 of the descriptor, which is what a TMA copy with
-// CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B writes.  Its atom is 4 rows (512 bytes), so K = 8 spans
-// two atoms: the stride byte offset (between groups of 4 rows) is 512; the leading byte
-// offset (between 128-byte column blocks) is never applied for N = 32.  Addresses and
-// strides are in 16-byte units; bits 46-47 = 1 is the descriptor version of sm_100.
-__device__ __forceinline__ uint64_t umma_desc_mn_tf32(uint32_t smem_addr)
+// Shared-memory descriptor of an MN-major TF32 operand: (n_blocks x 32) values along MN by 8
+// rows along K.  MN-major 32-bit operands have one legal layout: 128-byte rows of 32 values
+// whose 32-byte chunks are XOR-ed with (row % 4) -- layout type 1 of the descriptor, which is
+// what a TMA copy with CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B writes.  Its atom is 4 rows
+// (512 bytes), so K = 8 spans two atoms `sbo_bytes` apart (512 when the k rows follow one
+// another); blocks of 32 values along MN are `lbo_bytes` apart (not applied when MN = 32).
+// The start address must be 512-byte aligned.  Addresses and strides are in 16-byte units;
+// bits 46-47 = 1 is the descriptor version of sm_100.
+__device__ __forceinline__ uint64_t umma_desc_mn_tf32(uint32_t smem_addr, uint32_t lbo_bytes = 512, uint32_t sbo_bytes = 512)
 {
     uint64_t d = static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu);
-    d |= static_cast<uint64_t>(512 >> 4) << 16;       // leading byte offset (unused)
-    d |= static_cast<uint64_t>(512 >> 4) << 32;       // stride byte offset: next 4 rows of K
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;   // leading byte offset: next 32 values along MN
+    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;   // stride byte offset: next 4 rows of K
     d |= 1ull << 46;
     d |= 1ull << 61;                                  // SWIZZLE_128B_BASE32B
     return d;
 }
 
-// Instruction descriptor of kind::tf32: FP32 accumulate, A and B TF32, A K-major (it comes
-// from Tensor Memory), B MN-major (n contiguous in shared memory), M x N tile.
-__host__ __device__ constexpr uint32_t umma_idesc_tf32(int m, int n)
+// Instruction descriptor of kind::tf32: FP32 accumulate, A and B TF32, B MN-major (n
+// contiguous in shared memory), M x N tile.  A is K-major when it comes from Tensor Memory;
+// a_mn_major = true for an A taken from shared memory with m contiguous.
+__host__ __device__ constexpr uint32_t umma_idesc_tf32(int m, int n, bool a_mn_major = false)
 {
-    return (1u << 4) | (2u << 7) | (2u << 10) | (1u << 16) | (static_cast<uint32_t>(n >> 3) << 17) |
-           (static_cast<uint32_t>(m >> 4) << 24);
+    return (1u << 4) | (2u << 7) | (2u << 10) | (a_mn_major ? (1u << 15) : 0u) | (1u << 16) |
+           (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
 // One thread: D[tmem] (+)= A[tmem] * B[smem], M x N x 8 TF32.
@@ -94,6 +95,19 @@ __device__ __forceinline__ void umma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, u
         "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t"
         "}\n"
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate ? 1u : 0u)
+        : "memory");
+}
+
+// One thread: D[tmem] (+)= A[smem] * B[smem], M x N x 8 TF32.
+__device__ __forceinline__ void umma_tf32_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate ? 1u : 0u)
         : "memory");
 }
 

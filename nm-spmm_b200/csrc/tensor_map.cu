@@ -41,4 +41,25 @@ cudaError_t encode_tensor_map_2d(CUtensorMap* map, const float* base, int cols, 
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
+// The same row-major [rows][cols] tensor seen as blocks of 32 columns: dimensions
+// {32 columns, rows, cols / 32 blocks}, box {32, box_rows, box_blocks}.  A box lands in
+// shared memory block after block, each block [box_rows][32] with its 32-byte chunks
+// swizzled within the 128-byte rows: the layout of an MN-major TF32 tensor-core operand
+// that is box_blocks * 32 values wide.  cols must be a multiple of 32 (a partial last block
+// would run on into the next row instead of reading as zeros).
+cudaError_t encode_tensor_map_blocks32(CUtensorMap* map, const float* base, int cols, int rows, int box_rows, int box_blocks)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return cudaErrorNotSupported;
+    if (cols % 32 != 0) return cudaErrorInvalidValue;
+    const cuuint64_t dims[3] = { 32, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(cols / 32) };
+    const cuuint64_t strides[2] = { static_cast<cuuint64_t>(cols) * sizeof(float), 32 * sizeof(float) };
+    const cuuint32_t box[3] = { 32, static_cast<cuuint32_t>(box_rows), static_cast<cuuint32_t>(box_blocks) };
+    const cuuint32_t elem[3] = { 1, 1, 1 };
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
 }  // namespace nmspmm
