@@ -107,19 +107,25 @@ int nmspmm_preprocess_high_host(int* column_info_host, int pruning_M, int prunin
 
 typedef struct nmspmm_gemm_desc {
     int M, N, K;
-    int n_keep;        /* kept rows per 32-window: 32, 16, 12 (LOW) / 8, 4 (HIGH); LOW also takes 8.
-                          The TF32 path runs 12:32 as pairs of windows and wants K % 64 == 0 for it. */
+    int n_keep;        /* kept rows per 32-window: 32, 16, 12 (LOW) / 8, 4 (HIGH); LOW also takes 8 */
     int format;        /* nmspmm_format */
     int layout_ns;     /* Ns the index buffers were packed for: 32, 64 or 128 */
     int path;          /* nmspmm_path */
     int split_k;       /* >=1: that many K slices per tile; 0: the library balances k windows over the SMs */
     int tile;          /* 0: chosen by the library; otherwise an nmspmm_tile id (testing / tuning) */
+    int vec_len;       /* 0 or 32: every 32 columns have their own index list (VEC_LEN of the reference,
+                          include/NM-SpMM.h:8).  64: the caller promises that the lists of columns 64 v .. 64 v + 31
+                          and 64 v + 32 .. 64 v + 63 are equal (a 64-wide vector stored in the reference's format as
+                          two equal 32-wide ones; N % 64 == 0).  The TF32 path then gathers once per 64 columns
+                          and reads only the even list; the FP32 path computes the same either way. */
 } nmspmm_gemm_desc;
 
 /* Bytes of scratch the multiply needs for this description (0 when every unit range is a
  * whole tile).  The scratch holds per-tile arrival counters followed by slots for tile
- * pieces; the counters must be zero before the first use (cudaMemset once) and are
- * left zero by every call. */
+ * pieces.  The caller need not initialise it and may hand the same buffer to multiplies of
+ * different descriptions one after the other on a stream: a multiply that uses the counters
+ * clears them itself (a cudaMemsetAsync on `stream` ahead of the kernel).  Two multiplies
+ * that overlap on the GPU need two buffers. */
 size_t nmspmm_gemm_workspace_bytes(const nmspmm_gemm_desc* desc);
 
 /* Replaces the eight nmGEMM_*_matrices_{low,high}_sparsity launchers

@@ -43,7 +43,7 @@ STATIC_SCRATCH_BYTES = 16 << 20     # NMSPMM_STATIC_SCRATCH_BYTES of include/nms
 
 class GemmDesc(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int) for n in
-                ("M", "N", "K", "n_keep", "format", "layout_ns", "path", "split_k", "tile")]
+                ("M", "N", "K", "n_keep", "format", "layout_ns", "path", "split_k", "tile", "vec_len")]
 
 
 class PlanInfo(ctypes.Structure):
@@ -211,8 +211,8 @@ def preprocess_high_device(DT, pruning_M: int, pruning_N: int, Ns: int, fuse_tra
 # The multiply.
 # ----------------------------------------------------------------------------------
 
-def make_desc(M, N, K, n_keep, fmt, layout_ns, path=PATH_FP32, split_k=0, tile=0) -> GemmDesc:
-    return GemmDesc(M, N, K, n_keep, fmt, layout_ns, path, split_k, tile)
+def make_desc(M, N, K, n_keep, fmt, layout_ns, path=PATH_FP32, split_k=0, tile=0, vec_len=0) -> GemmDesc:
+    return GemmDesc(M, N, K, n_keep, fmt, layout_ns, path, split_k, tile, vec_len)
 
 
 def plan(desc: GemmDesc) -> PlanInfo:
@@ -354,11 +354,13 @@ class NMSpMM:
     ``B`` (W, N) float32 and the packed ``D`` / ``column_info`` live on the device;
     ``matmul`` multiplies any (K, M) col-major ``A`` against them."""
 
-    def __init__(self, BT, DT, K: int, n_keep: int, layout_ns: int = 128, fmt: Optional[int] = None, device=None):
+    def __init__(self, BT, DT, K: int, n_keep: int, layout_ns: int = 128, fmt: Optional[int] = None, device=None,
+                 vec_len: int = VEC_LEN):
         torch = _torch()
         load_library()
         dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.K, self.n_keep, self.layout_ns = K, n_keep, layout_ns
+        self.vec_len = vec_len      # 64: adjacent pairs of index lists are equal (what the generators and prune_device produce)
         self.format = format_of(n_keep) if fmt is None else fmt
         self.B = torch.as_tensor(BT, dtype=torch.float32).to(dev).contiguous()
         self.W, self.N = self.B.shape
@@ -372,17 +374,17 @@ class NMSpMM:
 
     @classmethod
     def from_problem(cls, p: "formats.NMProblem", layout_ns: int = 128, fmt: Optional[int] = None, device=None):
-        return cls(p.BT, p.DT, p.K, p.n_keep, layout_ns, fmt, device)
+        return cls(p.BT, p.DT, p.K, p.n_keep, layout_ns, fmt, device, vec_len=p.vec_len)
 
     @classmethod
     def from_dense(cls, dense, n_keep: int, vec_len: int = 32, layout_ns: int = 128, fmt: Optional[int] = None):
         """Prune a dense (K, N) float32 CUDA weight to ``n_keep``:32 by per-vector L2 magnitude,
         compress and pack it, all on the device (prune_device, then the packing kernels)."""
         BT, DT = prune_device(dense, n_keep, vec_len)
-        return cls(BT, DT, dense.shape[0], n_keep, layout_ns, fmt, dense.device)
+        return cls(BT, DT, dense.shape[0], n_keep, layout_ns, fmt, dense.device, vec_len=vec_len)
 
     def desc(self, M: int, path: int = PATH_FP32, split_k: int = 0, tile: int = 0) -> GemmDesc:
-        return make_desc(M, self.N, self.K, self.n_keep, self.format, self.layout_ns, path, split_k, tile)
+        return make_desc(M, self.N, self.K, self.n_keep, self.format, self.layout_ns, path, split_k, tile, self.vec_len)
 
     def _scratch(self, nbytes: int):
         torch = _torch()

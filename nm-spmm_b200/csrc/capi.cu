@@ -107,6 +107,8 @@ static int check_desc(const nmspmm_gemm_desc* d, int* mode_out)
     if (d->layout_ns != 32 && d->layout_ns != 64 && d->layout_ns != 128) return NMSPMM_INVALID_ARGUMENT;
     if (d->N % d->layout_ns != 0) return NMSPMM_INVALID_ARGUMENT;
     if (d->split_k < 0) return NMSPMM_INVALID_ARGUMENT;
+    if (d->vec_len != 0 && d->vec_len != 32 && d->vec_len != 64) return NMSPMM_INVALID_ARGUMENT;
+    if (d->vec_len == 64 && d->N % 64 != 0) return NMSPMM_INVALID_ARGUMENT;
     if (d->format == NMSPMM_FORMAT_LOW) {
         if (d->n_keep != 32 && d->n_keep != 16 && d->n_keep != 12 && d->n_keep != 8) return NMSPMM_UNSUPPORTED;
         *mode_out = kModeLow;
@@ -145,8 +147,16 @@ static int make_plan(const nmspmm_gemm_desc* d, int sms, Plan* p)
         int want_ns = (((d->N + 255) / 256) * ((d->M + 127) / 128) >= sms) ? 256 : 128;
         if (d->tile == kTile128x256) want_ns = 256;
         if (d->tile == kTile128x128) want_ns = 128;
-        for (int i = 0; i < kTf32VariantCount; ++i)
-            if (kTf32Variants[i].n_keep == d->n_keep && kTf32Variants[i].mode == mode && kTf32Variants[i].ns == want_ns)
+        // 64-wide vectors: the variants that gather once per 64 columns exist for tile 128 x 256
+        if (d->vec_len == 64 && d->tile != kTile128x128)
+            for (int i = 0; i < kTf32VariantCount; ++i)
+                if (kTf32Variants[i].n_keep == d->n_keep && kTf32Variants[i].mode == mode && kTf32Variants[i].vec_len == 64) {
+                    p->tv = &kTf32Variants[i];
+                    want_ns = p->tv->ns;
+                }
+        for (int i = 0; i < kTf32VariantCount && !p->tv; ++i)
+            if (kTf32Variants[i].n_keep == d->n_keep && kTf32Variants[i].mode == mode && kTf32Variants[i].vec_len == 32 &&
+                kTf32Variants[i].ns == want_ns)
                 p->tv = &kTf32Variants[i];
         if (!p->tv) return NMSPMM_UNSUPPORTED;
         p->ws = p->tv->ws;
@@ -546,6 +556,13 @@ static int gemm_launch(const nmspmm_gemm_desc* desc, const float* A_dev, const f
         if (workspace_bytes < p.counters_bytes + p.partial_bytes) return NMSPMM_WORKSPACE_TOO_SMALL;
         a.counters = p.deferred ? nullptr : static_cast<unsigned*>(workspace_dev);
         a.partial = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace_dev) + p.counters_bytes);
+        if (a.counters) {
+            // Where the counters end and the slots begin depends on the plan (tile count, path,
+            // split), so a buffer that served another plan may hold slot data here.  Clear the
+            // counters on the stream ahead of every launch that reads them.
+            cudaError_t me = cudaMemsetAsync(workspace_dev, 0, p.counters_bytes, static_cast<cudaStream_t>(stream));
+            if (me != cudaSuccess) return cuda_fail(me);
+        }
     }
     const bool plain = (n_out == 1 && ldc == desc->N && col0 == 0);
     cudaError_t e = p.v ? (plain ? p.v->launch : p.v->launch_multi)(a, outs, p.grid, static_cast<cudaStream_t>(stream))
@@ -635,18 +652,8 @@ int nmspmm_gemm_static_scratch(const nmspmm_gemm_desc* desc, const float* A_dev,
         }
         scratch = g_static_scratch_ptr[dev];
     }
-    if (need > 0) {
-        // the arrival counters at the head of the scratch must read zero; the slots behind
-        // them are fully written before they are read
-        Plan p;
-        DeviceInfo* di = nullptr;
-        int rc = device_info(&di);
-        if (rc != NMSPMM_OK) return rc;
-        rc = make_plan(desc, di->sms, &p);
-        if (rc != NMSPMM_OK) return rc;
-        e = cudaMemsetAsync(scratch, 0, p.counters_bytes, static_cast<cudaStream_t>(stream));
-        if (e != cudaSuccess) return cuda_fail(e);
-    }
+    // (the arrival counters at the head of the scratch are cleared on the stream by the
+    // multiply itself; the slots behind them are fully written before they are read)
     return nmspmm_gemm(desc, A_dev, B_dev, D_dev, column_info_dev, C_dev, need ? scratch : nullptr, need, stream);
 }
 
@@ -672,7 +679,7 @@ int nmspmm_gemm_host(const nmspmm_gemm_desc* desc, const float* A_host, const fl
     if (n_chunks < 1) n_chunks = 1;
     const int chunk_rows = (M / n_chunks + 127) / 128 * 128;
     n_chunks = (M + chunk_rows - 1) / chunk_rows;
-    size_t ws_need = 0, counters_need = 0;
+    size_t ws_need = 0;
     for (int c = 0; c < n_chunks; ++c) {
         nmspmm_gemm_desc dc = *desc;
         dc.M = (c + 1 < n_chunks) ? chunk_rows : M - c * chunk_rows;
@@ -680,7 +687,6 @@ int nmspmm_gemm_host(const nmspmm_gemm_desc* desc, const float* A_host, const fl
         rc = make_plan(&dc, di->sms, &pc);
         if (rc != NMSPMM_OK) return rc;
         if (pc.counters_bytes + pc.partial_bytes > ws_need) ws_need = pc.counters_bytes + pc.partial_bytes;
-        if (pc.counters_bytes > counters_need) counters_need = pc.counters_bytes;
     }
 
     const size_t a_b = round256(sizeof(float) * M * static_cast<size_t>(K));
@@ -723,7 +729,6 @@ int nmspmm_gemm_host(const nmspmm_gemm_desc* desc, const float* A_host, const fl
     else
         rc = nmspmm_preprocess_low_device(dDT, dD, W, Q, desc->layout_ns, st);
     if (rc != NMSPMM_OK) return rc;
-    if (counters_need > 0) NMSPMM_TRY(cudaMemsetAsync(dWS, 0, counters_need, st));   // the counters at the head of the scratch
     for (int c = 0; c < n_chunks; ++c) {
         const int r0 = c * chunk_rows, rows = (c + 1 < n_chunks) ? chunk_rows : M - r0;
         nmspmm_gemm_desc dc = *desc;

@@ -61,7 +61,7 @@ __device__ unsigned long long g_tf32_profile[16];
 #define TF_OUT(i, v)
 #endif
 
-template <int NKEEP, int KW_, int MODE, int QT_>
+template <int NKEEP, int KW_, int MODE, int QT_, int VL_ = 32>
 struct Tf32Cfg {
     static constexpr int MS = 128, QT = QT_, NS = QT * 32;   // QT = 8: one CTA per SM; QT = 4: two
     static constexpr int KW = KW_;                           // k per step
@@ -70,7 +70,10 @@ struct Tf32Cfg {
     static constexpr bool DIRECT = (NKEEP == 32);            // identity index list: no gather
     static constexpr int G = WSP / 8;                        // product instructions per vector and step
     static constexpr int NKS = KW / 8;                       // gather instructions per step
-    static constexpr int N1 = QT * WSP;                      // gathered columns per step
+    static constexpr int VL = VL_;                           // columns that share an index list: 32, or 64 (two adjacent equal lists)
+    static constexpr int QV = NS / VL;                       // vectors per tile
+    static constexpr int N1 = QV * WSP;                      // gathered columns per step
+    static_assert(VL == 32 || (VL == 64 && NKEEP != 32), "vectors of 32 or 64 columns");
     static_assert(DIRECT || N1 <= 128, "one builder thread per gathered column");
     static_assert(MODE == kModeHigh || KW == 32, "only the 64-k format has merged windows");
     static constexpr int A_BYTES = KW * 512;                 // [4 blocks of 32 rows of the tile][KW][32]
@@ -112,13 +115,14 @@ __device__ __forceinline__ uint32_t p_offset(int n, int k)
     return static_cast<uint32_t>(nb * (KW * 128) + k * 128 + ((((c >> 3) ^ (k & 3)) << 5) | ((c & 7) << 2)));
 }
 
-template <int NKEEP, int KW_, int MODE, int QT_>
-__global__ void __launch_bounds__((Tf32Cfg<NKEEP, KW_, MODE, QT_>::THREADS), (Tf32Cfg<NKEEP, KW_, MODE, QT_>::CTAS_PER_SM))
+template <int NKEEP, int KW_, int MODE, int QT_, int VL_>
+__global__ void __launch_bounds__((Tf32Cfg<NKEEP, KW_, MODE, QT_, VL_>::THREADS), (Tf32Cfg<NKEEP, KW_, MODE, QT_, VL_>::CTAS_PER_SM))
 nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const GemmOutputs outs, const int a_blocked)
 {
-    using Cfg = Tf32Cfg<NKEEP, KW_, MODE, QT_>;
+    using Cfg = Tf32Cfg<NKEEP, KW_, MODE, QT_, VL_>;
     constexpr int MS = Cfg::MS, NS = Cfg::NS, QT = Cfg::QT, KW = Cfg::KW, WS = Cfg::WS, WSP = Cfg::WSP;
+    constexpr int VL = Cfg::VL, QV = Cfg::QV, BPV = VL / 32;              // 32-column blocks per vector
     constexpr int STAGES = Cfg::STAGES, NBUF = Cfg::NBUF, RING = Cfg::RING, PD = Cfg::PD;
     constexpr bool DIRECT = Cfg::DIRECT;
     constexpr int FIRST_BUILDER = 2 + Cfg::PRODUCT_WARPS;
@@ -236,8 +240,12 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
                     tc_commit(bar_empty + s * 8);
                 } else {
                     const uint32_t gbuf = tmem_addr(tmem, 0, Cfg::ACOL0 + (t % NBUF) * Cfg::N1);
+#ifdef NMSPMM_TF32_SKIP_G
+                    for (int ks = 0; ks < 1; ++ks)
+#else
 #pragma unroll
                     for (int ks = 0; ks < Cfg::NKS; ++ks)
+#endif
                         umma_tf32_ss(gbuf, umma_desc_mn_tf32(st + ks * 1024, KW * 128, 512),
                                      umma_desc_mn_tf32(st + Cfg::A_BYTES + Cfg::B_BYTES + ks * 1024, KW * 128, 512),
                                      idesc_gather, ks != 0);
@@ -260,9 +268,9 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
     } else if (warp < FIRST_BUILDER) {
         // ------------------------------------------------------------------ product issuers
         if (!DIRECT) {
-            constexpr uint32_t idesc_product = umma_idesc_tf32(128, 32, false);
-            constexpr int VPI = QT / Cfg::PRODUCT_WARPS;   // vectors per issuer
-            const int v_begin = (warp - 2) * VPI, v_end = min(v_begin + VPI, live_vecs);
+            constexpr uint32_t idesc_product = umma_idesc_tf32(128, VL, false);
+            constexpr int VPI = QV / Cfg::PRODUCT_WARPS;   // vectors per issuer
+            const int v_begin = (warp - 2) * VPI, v_end = min(v_begin + VPI, live_vecs / BPV);
             bool alive = true;
             TF_DECL(c_gdone = 0, c_issue = 0);
             TF_T(c_start);
@@ -280,11 +288,16 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
                     if (v_begin < v_end) {
                         const uint32_t bs = ring + s * Cfg::STAGE_BYTES + Cfg::A_BYTES;
                         const uint32_t gbuf = tmem_addr(tmem, 0, Cfg::ACOL0 + b * Cfg::N1);
+#ifdef NMSPMM_TF32_SKIP_C
+                        for (int v = v_begin; v < v_begin + 1; ++v) {
+#else
                         for (int v = v_begin; v < v_end; ++v) {
+#endif
 #pragma unroll
                             for (int gi = 0; gi < Cfg::G; ++gi)
-                                umma_tf32_ts(tmem_addr(tmem, 0, v * 32), gbuf + v * WSP + gi * 8,
-                                             umma_desc_mn_tf32(bs + v * (WSP * 128) + gi * 1024), idesc_product, (u | gi) != 0);
+                                umma_tf32_ts(tmem_addr(tmem, 0, v * VL), gbuf + v * WSP + gi * 8,
+                                             umma_desc_mn_tf32(bs + v * (BPV * WSP * 128) + gi * 1024, WSP * 128, 512),
+                                             idesc_product, (u | gi) != 0);
                         }
                         tc_commit(bar_empty + s * 8);      // this half of the step's products has read the stage and the gather result
                     } else {
@@ -310,8 +323,8 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
         bool alive = true;
         if (!DIRECT) {
             const int v = e / WSP, j = e % WSP;
-            const bool has = e < Cfg::N1 && j < WS && v < live_vecs;
-            const int q = (bj >> 5) + v, qs_shift = g.qs_shift;
+            const bool has = e < Cfg::N1 && j < WS && v * BPV < live_vecs;
+            const int q = (bj >> 5) + v * BPV, qs_shift = g.qs_shift;       // the (first) 32-column index list of vector v
             const int* dptr = g.D + ((static_cast<size_t>(q >> qs_shift) * g.W) << qs_shift) + (q & ((1 << qs_shift) - 1)) +
                               (static_cast<size_t>(j) << qs_shift);
             const int n_merged = (KW == 64) ? g.sched.n_win : (g.sched.n_win >> 1);
@@ -419,11 +432,11 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
     }
 }
 
-template <int NKEEP, int KW, int MODE, int QT>
+template <int NKEEP, int KW, int MODE, int QT, int VL>
 static cudaError_t launch_tf32(const GemmArgs& a, const GemmOutputs& outs, int tiles, cudaStream_t st)
 {
-    using Cfg = Tf32Cfg<NKEEP, KW, MODE, QT>;
-    auto kernel = nm_gemm_tf32_kernel<NKEEP, KW, MODE, QT>;
+    using Cfg = Tf32Cfg<NKEEP, KW, MODE, QT, VL>;
+    auto kernel = nm_gemm_tf32_kernel<NKEEP, KW, MODE, QT, VL>;
     static bool configured[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -445,17 +458,21 @@ static cudaError_t launch_tf32(const GemmArgs& a, const GemmOutputs& outs, int t
     return cudaGetLastError();
 }
 
-#define NMSPMM_TF32_VARIANT(NKEEP, KW, MODE, QT)                                                                   \
-    { NKEEP, Tf32Cfg<NKEEP, KW, MODE, QT>::WS, KW, MODE, QT * 32, Tf32Cfg<NKEEP, KW, MODE, QT>::SMEM_BYTES,        \
-      Tf32Cfg<NKEEP, KW, MODE, QT>::STAGES, Tf32Cfg<NKEEP, KW, MODE, QT>::THREADS, &launch_tf32<NKEEP, KW, MODE, QT> }
+#define NMSPMM_TF32_VARIANT(NKEEP, KW, MODE, QT, VL)                                                                   \
+    { NKEEP, Tf32Cfg<NKEEP, KW, MODE, QT, VL>::WS, KW, MODE, QT * 32, VL, Tf32Cfg<NKEEP, KW, MODE, QT, VL>::SMEM_BYTES,    \
+      Tf32Cfg<NKEEP, KW, MODE, QT, VL>::STAGES, Tf32Cfg<NKEEP, KW, MODE, QT, VL>::THREADS, &launch_tf32<NKEEP, KW, MODE, QT, VL> }
 
 extern const Tf32Variant kTf32Variants[] = {
-    NMSPMM_TF32_VARIANT(32, 32, kModeLow, 8),  NMSPMM_TF32_VARIANT(32, 32, kModeLow, 4),
-    NMSPMM_TF32_VARIANT(16, 32, kModeLow, 8),  NMSPMM_TF32_VARIANT(16, 32, kModeLow, 4),
-    NMSPMM_TF32_VARIANT(12, 32, kModeLow, 8),  NMSPMM_TF32_VARIANT(12, 32, kModeLow, 4),
-    NMSPMM_TF32_VARIANT(8, 32, kModeLow, 8),   NMSPMM_TF32_VARIANT(8, 32, kModeLow, 4),
-    NMSPMM_TF32_VARIANT(8, 32, kModeHigh, 8),  NMSPMM_TF32_VARIANT(8, 32, kModeHigh, 4),
-    NMSPMM_TF32_VARIANT(4, 64, kModeHigh, 8),  NMSPMM_TF32_VARIANT(4, 64, kModeHigh, 4),
+    NMSPMM_TF32_VARIANT(32, 32, kModeLow, 8, 32),  NMSPMM_TF32_VARIANT(32, 32, kModeLow, 4, 32),
+    NMSPMM_TF32_VARIANT(16, 32, kModeLow, 8, 32),  NMSPMM_TF32_VARIANT(16, 32, kModeLow, 4, 32),
+    NMSPMM_TF32_VARIANT(12, 32, kModeLow, 8, 32),  NMSPMM_TF32_VARIANT(12, 32, kModeLow, 4, 32),
+    NMSPMM_TF32_VARIANT(8, 32, kModeLow, 8, 32),   NMSPMM_TF32_VARIANT(8, 32, kModeLow, 4, 32),
+    NMSPMM_TF32_VARIANT(8, 32, kModeHigh, 8, 32),  NMSPMM_TF32_VARIANT(8, 32, kModeHigh, 4, 32),
+    NMSPMM_TF32_VARIANT(4, 64, kModeHigh, 8, 32),  NMSPMM_TF32_VARIANT(4, 64, kModeHigh, 4, 32),
+    // vectors of 64 columns (two adjacent equal index lists): one gather and one N = 64 product per pair
+    NMSPMM_TF32_VARIANT(16, 32, kModeLow, 8, 64),  NMSPMM_TF32_VARIANT(12, 32, kModeLow, 8, 64),
+    NMSPMM_TF32_VARIANT(8, 32, kModeLow, 8, 64),   NMSPMM_TF32_VARIANT(8, 32, kModeHigh, 8, 64),
+    NMSPMM_TF32_VARIANT(4, 64, kModeHigh, 8, 64),
 };
 extern const int kTf32VariantCount = sizeof(kTf32Variants) / sizeof(kTf32Variants[0]);
 

@@ -44,6 +44,7 @@ struct Tf32Variant {
     int ws, ks;         // rows of B / of A per step
     int mode;
     int ns;             // tile columns: 256 (one CTA per SM) or 128 (two)
+    int vec_len;        // columns that share an index list: 32, or 64 (adjacent equal lists)
     int smem_bytes, stages, threads;
     cudaError_t (*launch)(const GemmArgs&, const GemmOutputs&, int tiles, cudaStream_t st);
 };

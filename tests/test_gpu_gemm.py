@@ -218,3 +218,31 @@ def test_large_sharded_full_size(pkg, orc):
         ref = full[:, c0:c1]
         assert float((slab - ref).norm() / ref.norm()) <= 1e-6, rank
     assert pkg.device_status() == 0
+
+
+def test_one_scratch_buffer_serves_different_plans_in_turn(pkg):
+    """The boundary between arrival counters and slots moves with the plan.  One operator
+    (one cached scratch buffer) multiplies 512, 128 and 512 rows, then FP32, TF32, FP32:
+    the slots of one plan land on the counters of the other, and every result must still
+    be complete.  Checked against whole-tile launches (no scratch at all)."""
+    p = pkg.formats.make_random(512, 4096, 4096, 8, seed=77)
+    op = pkg.NMSpMM.from_problem(p)
+    ref_op = pkg.NMSpMM.from_problem(p)
+    A = torch.from_numpy(p.A_km).cuda()
+    plans = [pkg.plan(op.desc(m)) for m in (512, 128)]
+    assert any(pl.n_virtual > pl.n_dp for pl in plans), "at least one of the two plans must split tiles"
+
+    def check(rows, path):
+        a = A[:, :rows].contiguous()
+        got = op.matmul(a, path=path, out=torch.full((rows, 4096), float("nan"), device="cuda"))
+        want = ref_op.matmul(a, path=path, split_k=1)
+        torch.cuda.synchronize()
+        assert pkg.device_status() == 0
+        err = float((got.double() - want.double()).norm() / want.double().norm())
+        assert err <= (FP32_TOL if path == pkg.PATH_FP32 else 2e-3), (rows, path, err)
+        assert not bool(torch.isnan(got).any())
+
+    for rows in (512, 128, 512, 128, 512):
+        check(rows, pkg.PATH_FP32)
+    for path in (pkg.PATH_FP32, pkg.PATH_TF32, pkg.PATH_FP32, pkg.PATH_TF32, pkg.PATH_FP32):
+        check(384, path)

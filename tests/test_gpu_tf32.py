@@ -103,3 +103,17 @@ def test_tf32_square_4096_full_size(pkg, orc, n_keep):
     exact = op.matmul(A)
     assert float((C - exact).norm() / exact.norm()) <= TF32_TOL
     assert pkg.device_status() == 0
+
+
+@pytest.mark.parametrize("n_keep,fmt", [(16, 0), (12, 0), (8, 0), (8, 1), (4, 1)])
+@pytest.mark.parametrize("M,N,K", [(256, 512, 512), (200, 640, 256), (128, 64, 64)])
+def test_tf32_vectors_of_64_columns(pkg, orc, n_keep, fmt, M, N, K):
+    """vec_len = 64: adjacent pairs of 32-wide index lists are equal and the kernel gathers
+    once per 64 columns (N = 64 products).  Ragged last tile (640 = 2 x 256 + 128)."""
+    p = pkg.formats.make_random(M, N, K, n_keep, seed=220 + n_keep, vec_len=64)
+    op = pkg.NMSpMM.from_problem(p, fmt=fmt, layout_ns=128 if N % 128 == 0 else 64)
+    assert op.vec_len == 64 and op.desc(M, path=pkg.PATH_TF32).vec_len == 64
+    C = op.matmul(torch.from_numpy(p.A_km).cuda(), path=pkg.PATH_TF32)
+    torch.cuda.synchronize()
+    assert pkg.device_status() == 0
+    assert rel_err(C.cpu().numpy(), orc.nm_gemm_f64(p.A_km, p.B_col, p.D_col)) <= TF32_TOL

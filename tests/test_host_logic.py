@@ -122,7 +122,9 @@ def test_split_k_fills_the_machine_for_skinny_shapes(pkg):
     tbig = pkg.plan(pkg.make_desc(4096, 4096, 4096, 8, 1, 128, path=pkg.PATH_TF32))
     assert tbig.tile_n == 256 and tbig.n_dp == 444 and tbig.split_k == 2 and tbig.grid == 444 + 2 * 68
     tlow = pkg.plan(pkg.make_desc(4096, 4096, 4096, 16, 0, 128, path=pkg.PATH_TF32))
-    assert tlow.tile_n == 128 and tlow.split_k == 1 and tlow.grid == 1024      # two CTAs per SM: the last wave stays whole
+    assert tlow.tile_n == 256 and tlow.n_dp == 444 and tlow.grid == 444 + 2 * 68   # the wide tile for every ratio once it fills the GPU
+    tsmall = pkg.plan(pkg.make_desc(1024, 2048, 4096, 16, 0, 128, path=pkg.PATH_TF32))
+    assert tsmall.tile_n == 128                                                # 64 wide tiles would leave SMs idle: the narrow one
     texact = pkg.plan(pkg.make_desc(128 * 148, 256, 4096, 8, 1, 128, path=pkg.PATH_TF32))    # exactly one wave: nothing to slice
     assert texact.split_k == 1 and texact.grid == 148 and pkg.workspace_bytes(pkg.make_desc(128 * 148, 256, 4096, 8, 1, 128, path=pkg.PATH_TF32)) == 0
     one = pkg.plan(pkg.make_desc(128, 128, 64, 16, 0, 128, split_k=1))
@@ -131,14 +133,14 @@ def test_split_k_fills_the_machine_for_skinny_shapes(pkg):
 
 @pytest.mark.parametrize("kw,status", [
     (dict(M=0), 1), (dict(N=100), 1), (dict(K=48), 1), (dict(M=6), 1), (dict(layout_ns=96), 1),
-    (dict(n_keep=10), 2), (dict(n_keep=16, fmt=1), 2), (dict(n_keep=4, fmt=0), 2), (dict(path=2), 2), (dict(path=1, n_keep=12, K=96), 2),
+    (dict(n_keep=10), 2), (dict(n_keep=16, fmt=1), 2), (dict(n_keep=4, fmt=0), 2), (dict(path=2), 2), (dict(vec_len=48), 1), (dict(vec_len=64, N=160, layout_ns=32), 1),
     (dict(N=192, layout_ns=128), 1), (dict(K=96, n_keep=8, fmt=1), 1), (dict(split_k=-1), 1),
 ])
 def test_bad_descriptions_are_rejected(pkg, kw, status):
-    base = dict(M=128, N=256, K=256, n_keep=16, fmt=0, layout_ns=128, path=0, split_k=0)
+    base = dict(M=128, N=256, K=256, n_keep=16, fmt=0, layout_ns=128, path=0, split_k=0, vec_len=0)
     base.update(kw)
     d = pkg.make_desc(base["M"], base["N"], base["K"], base["n_keep"], base["fmt"], base["layout_ns"],
-                      base["path"], base["split_k"])
+                      base["path"], base["split_k"], 0, base["vec_len"])
     info = pkg.PlanInfo()
     rc = pkg.load_library().nmspmm_gemm_plan(ctypes.byref(d), ctypes.byref(info))
     assert rc == status, (kw, rc)
