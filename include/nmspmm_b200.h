@@ -174,9 +174,13 @@ int nmspmm_gemm_with_cached_workspace(const nmspmm_gemm_desc* desc,
  * held until the process exits.  The call is nmspmm_gemm with that array as workspace; it
  * calls no cudaMalloc, cudaFree or other allocating routine.
  *
- *  - Descriptions whose nmspmm_gemm_workspace_bytes exceeds NMSPMM_STATIC_SCRATCH_BYTES are
- *    rejected with NMSPMM_WORKSPACE_TOO_SMALL and a message on stderr (nothing is launched);
- *    an explicit, smaller split_k lowers the need.
+ *  - With split_k = 0 the library first tries its automatic schedule; where that wants more
+ *    than the array holds (it sizes its ranges for the machine: two slots per resident CTA)
+ *    it falls back to the largest number of equal K slices per tile whose slots fit, down
+ *    to whole tiles, which need no scratch.  The result is the same sum in a different
+ *    order; it can be slower than nmspmm_gemm with caller scratch on skinny or deep-K shapes.
+ *  - An explicit split_k whose slots exceed NMSPMM_STATIC_SCRATCH_BYTES is rejected with
+ *    NMSPMM_WORKSPACE_TOO_SMALL and a message on stderr (nothing is launched).
  *  - The first call on a device looks the array's address up (cudaGetSymbolAddress, with
  *    that device current) and keeps it; make that first call before any stream capture.
  *  - Every call uses the same array and it keeps the previous call's contents.  The
@@ -230,6 +234,16 @@ int nmspmm_release_cached(void);
  * scalar FFMA, packed = 1 the two-lane packed FMA of sm_100.  The FP32 roofline
  * denominator is the larger of the two. */
 int nmspmm_measure_ffma_peak(double* tflops_out, int packed, void* stream);
+
+/* ------------------------------------------------------------------ testing
+ * Makes the bounded device-side waits run out without faulting or hanging anything: while
+ * enabled, the multiply's launchers encode the tensor map of B with a box one row short, so
+ * every stage receives fewer bytes than its mbarrier expects.  The kernels themselves are
+ * unchanged: each wait gives up after about a second of SM clock, the CTA leaves through
+ * its barriers without storing, C keeps its contents and nmspmm_device_status reports
+ * NMSPMM_DEVICE_TIMEOUT.  Returns the previous setting.  Process-wide; for tests only (use a
+ * problem of a few tiles: every CTA waits its second out). */
+int nmspmm_test_short_fill(int enable);
 
 #ifdef __cplusplus
 }

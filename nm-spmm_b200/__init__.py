@@ -34,7 +34,7 @@ C_ABI_SYMBOLS = (
     "nmspmm_status_string", "nmspmm_last_cuda_error", "nmspmm_version",
     "nmspmm_trans_index_device", "nmspmm_preprocess_low_device", "nmspmm_preprocess_high_device",
     "nmspmm_trans_index_host", "nmspmm_preprocess_low_host", "nmspmm_preprocess_high_host",
-    "nmspmm_gemm_workspace_bytes", "nmspmm_gemm", "nmspmm_gemm_with_cached_workspace", "nmspmm_device_status",
+    "nmspmm_test_short_fill", "nmspmm_gemm_workspace_bytes", "nmspmm_gemm", "nmspmm_gemm_with_cached_workspace", "nmspmm_device_status",
     "nmspmm_gemm_plan", "nmspmm_gemm_host", "nmspmm_release_cached", "nmspmm_measure_ffma_peak",
     "nmspmm_gemm_static_scratch", "nmspmm_gemm_gather", "nmspmm_prune_device",
 )
@@ -289,6 +289,12 @@ def device_status(clear: bool = True) -> int:
     if rc not in (OK, DEVICE_TIMEOUT):
         raise NMSpMMError("nmspmm_device_status", rc)
     return word.value
+
+
+def test_short_fill(enable: bool) -> int:
+    """Test hook: while on, the multiply's stages never fill and its bounded waits run out
+    (nmspmm_test_short_fill).  Returns the previous setting."""
+    return int(load_library().nmspmm_test_short_fill(1 if enable else 0))
 
 
 def _launcher(layout_ns: int, high: bool):

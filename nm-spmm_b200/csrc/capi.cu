@@ -34,6 +34,8 @@ const FfmaVariant* find_ffma_variant(int tile_id, int n_keep, int mode)
     return nullptr;
 }
 
+int g_test_short_fill = 0;
+
 static thread_local int tl_last_cuda_error = 0;
 
 static int cuda_fail(cudaError_t e)
@@ -53,9 +55,6 @@ struct DeviceInfo {
 static DeviceInfo g_dev[64];
 static std::mutex g_dev_mutex;
 __device__ int g_status_word;      // raised by kernels whose bounded waits gave up
-#ifdef NMSPMM_PROFILE_WAITS
-__device__ unsigned long long g_wait_profile[8];   // diagnostic build: wait, fill, total cycles of warp 0, CTA count, epilogue sum / max, total max
-#endif
 
 static int device_info(DeviceInfo** out)
 {
@@ -632,12 +631,34 @@ int nmspmm_gemm_static_scratch(const nmspmm_gemm_desc* desc, const float* A_dev,
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e);
     if (dev < 0 || dev >= 64) return NMSPMM_UNSUPPORTED;
-    const size_t need = nmspmm_gemm_workspace_bytes(desc);
+    if (!desc) return NMSPMM_INVALID_ARGUMENT;
+    nmspmm_gemm_desc d = *desc;
+    size_t need = nmspmm_gemm_workspace_bytes(&d);
+    if (need > static_cast<size_t>(NMSPMM_STATIC_SCRATCH_BYTES) && desc->split_k == 0) {
+        // The automatic schedule sizes its ranges for the machine, not for this array (two
+        // slots per resident CTA).  Fall back to the largest number of equal K slices per
+        // tile whose slots fit; a single slice is a whole tile and needs no scratch at all.
+        Plan p;
+        DeviceInfo* di = nullptr;
+        int rc = device_info(&di);
+        if (rc != NMSPMM_OK) return rc;
+        rc = make_plan(desc, di->sms, &p);
+        if (rc != NMSPMM_OK) return rc;
+        const size_t per_slot = p.slots > 0 ? p.partial_bytes / static_cast<size_t>(p.slots) : 0;
+        long long s = per_slot ? static_cast<long long>(NMSPMM_STATIC_SCRATCH_BYTES / (per_slot * static_cast<size_t>(p.n_tiles))) : 1;
+        if (s > p.n_win) s = p.n_win;
+        for (; s >= 1; --s) {
+            d.split_k = static_cast<int>(s);
+            need = nmspmm_gemm_workspace_bytes(&d);
+            if (need <= static_cast<size_t>(NMSPMM_STATIC_SCRATCH_BYTES)) break;
+        }
+        if (s < 1) d.split_k = 1, need = nmspmm_gemm_workspace_bytes(&d);
+    }
     if (need > static_cast<size_t>(NMSPMM_STATIC_SCRATCH_BYTES)) {
         fprintf(stderr,
-                "nmspmm_gemm_static_scratch: this multiply needs %zu bytes of scratch, the built-in array holds %zu; "
-                "pass a smaller split_k or use nmspmm_gemm with caller scratch\n",
-                need, static_cast<size_t>(NMSPMM_STATIC_SCRATCH_BYTES));
+                "nmspmm_gemm_static_scratch: split_k = %d needs %zu bytes of scratch, the built-in array holds %zu; "
+                "pass a smaller split_k (0 lets the library pick one that fits) or use nmspmm_gemm with caller scratch\n",
+                desc->split_k, need, static_cast<size_t>(NMSPMM_STATIC_SCRATCH_BYTES));
         return NMSPMM_WORKSPACE_TOO_SMALL;
     }
     void* scratch = nullptr;
@@ -654,7 +675,7 @@ int nmspmm_gemm_static_scratch(const nmspmm_gemm_desc* desc, const float* A_dev,
     }
     // (the arrival counters at the head of the scratch are cleared on the stream by the
     // multiply itself; the slots behind them are fully written before they are read)
-    return nmspmm_gemm(desc, A_dev, B_dev, D_dev, column_info_dev, C_dev, need ? scratch : nullptr, need, stream);
+    return nmspmm_gemm(&d, A_dev, B_dev, D_dev, column_info_dev, C_dev, need ? scratch : nullptr, need, stream);
 }
 
 int nmspmm_gemm_host(const nmspmm_gemm_desc* desc, const float* A_host, const float* B_host, const int* DT_host,
@@ -749,17 +770,12 @@ int nmspmm_gemm_host(const nmspmm_gemm_desc* desc, const float* A_host, const fl
     return nmspmm_device_status(nullptr, 1);
 }
 
-#ifdef NMSPMM_PROFILE_WAITS
-// Diagnostic build only: reads and clears the cycle counters.
-int nmspmm_debug_wait_profile(unsigned long long* out8)
+int nmspmm_test_short_fill(int enable)
 {
-    cudaError_t e = cudaMemcpyFromSymbol(out8, g_wait_profile, sizeof(unsigned long long) * 8);
-    if (e != cudaSuccess) return cuda_fail(e);
-    unsigned long long zero[8] = {};
-    e = cudaMemcpyToSymbol(g_wait_profile, zero, sizeof(zero));
-    return e == cudaSuccess ? NMSPMM_OK : cuda_fail(e);
+    const int was = g_test_short_fill;
+    g_test_short_fill = enable ? 1 : 0;
+    return was;
 }
-#endif
 
 int nmspmm_release_cached(void)
 {

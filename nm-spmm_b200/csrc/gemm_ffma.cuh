@@ -40,23 +40,11 @@
 
 namespace nmspmm {
 
-// Diagnostic build (-DNMSPMM_PROFILE_WAITS): warp 0 of every CTA adds up the cycles
-// it spends waiting for a filled stage, filling a stage, and in total.
-#ifdef NMSPMM_PROFILE_WAITS
-extern __device__ unsigned long long g_wait_profile[8];
-#define NMSPMM_PROF_T(var) const long long var = clock64()
-#define NMSPMM_PROF_ADD(acc, t0) acc += clock64() - (t0)
-#else
-#define NMSPMM_PROF_T(var)
-#define NMSPMM_PROF_ADD(acc, t0)
-#endif
-
 template <int MS, int NS, int WM, int WS, int KS_, int MODE>
 struct FfmaCfg {
     static constexpr int KS = KS_;                       // rows of A staged per window: 32, or 64 (a merged HIGH window)
-    static constexpr bool HALF = (MODE == kModeHigh && KS_ == 32);   // HIGH staged by halves of the merged window
     static constexpr bool PAIR = (MODE == kModeLow && KS_ == 64);    // LOW staged as pairs of 32-k windows (WS = 2 n_keep)
-    static_assert(MODE == kModeHigh || KS_ == 32 || KS_ == 64, "LOW windows are 32 k wide, staged singly or in pairs");
+    static_assert(KS_ == 64 || (MODE == kModeLow && KS_ == 32), "LOW windows are 32 k wide, staged singly or in pairs; HIGH windows are 64 k wide");
     static constexpr int QT = NS / kVecLen;              // vectors per tile
     static constexpr int WARPS_M = MS / WM;
     static constexpr int NCW = QT * WARPS_M;             // warps (all of them compute)
@@ -152,9 +140,8 @@ __device__ __forceinline__ void nm_gemm_ffma_body(const GemmArgs& g, const CUten
             const int* src = g.D + ((static_cast<size_t>(lb0 + lane) * g.W) << qs_shift) + static_cast<size_t>(win) * d_chunk;
             bulk_g2s(ds + lane * d_bytes, src, d_bytes, full);
             if (MODE == kModeHigh) {
-                // one list per merged 64-k window: two staged windows share it when HALF
-                const int n_merged = Cfg::HALF ? (g.sched.n_win >> 1) : g.sched.n_win;
-                const int* ci = g.cinfo + (static_cast<size_t>(lb0 + lane) * n_merged + (Cfg::HALF ? (win >> 1) : win)) * 64;
+                // one list per merged 64-k window
+                const int* ci = g.cinfo + (static_cast<size_t>(lb0 + lane) * g.sched.n_win + win) * 64;
                 bulk_g2s(ds + Cfg::D_BYTES + lane * 256, ci, 256, full);
             }
         }
@@ -165,11 +152,8 @@ __device__ __forceinline__ void nm_gemm_ffma_body(const GemmArgs& g, const CUten
     for (int j = 0; j < STAGES - 1 && u_begin + j < u_end; ++j)
         if (j % NCW == warp) fill(j, u_begin + j);
 
-#ifdef NMSPMM_PROFILE_WAITS
-    long long prof_wait = 0, prof_fill = 0, prof_epi = 0;
-    const long long prof_start = clock64();
-#endif
     int s = 0, use = 0;                                    // stage of the window being multiplied, and its use count
+    bool alive = true;                                     // no wait of this warp has given up yet
     const uint32_t a_rel = (wm * WM + lm * (MT >= 4 ? 4 : 2)) * 4;
     const uint32_t b_rel = Cfg::A_BYTES + (vec * kVecLen + (lane >> 4) * 8 + (lane & 1) * 4) * 4;
 
@@ -177,7 +161,6 @@ __device__ __forceinline__ void nm_gemm_ffma_body(const GemmArgs& g, const CUten
     for (int cu = u_begin; cu < u_end;) {
         const int tile = cu / g.sched.n_win;
         const int piece_n = min((tile + 1) * g.sched.n_win, u_end) - cu;
-        const int win0 = cu - tile * g.sched.n_win;        // first window of the piece
         uint32_t d_rel, ci_rel;
         bool live;
         {
@@ -204,63 +187,39 @@ __device__ __forceinline__ void nm_gemm_ffma_body(const GemmArgs& g, const CUten
             __syncthreads();
             {
                 const int next = cu + w + STAGES - 1;
-                if (next < u_end && ((cu + w) % NCW) == warp) {
+                // (never re-arm a stage after a wait gave up: its barrier may still be in the
+                // phase that did not complete, and a second arrival would underflow its count)
+                if (next < u_end && ((cu + w) % NCW) == warp && alive) {
                     if (lane == 0) fence_proxy_async();    // the CTA's reads of the stage come before the TMA's writes
                     __syncwarp();
-                    NMSPMM_PROF_T(tf);
                     fill(s == 0 ? STAGES - 1 : s - 1, next);
-                    NMSPMM_PROF_ADD(prof_fill, tf);
                 }
             }
             // A wait that gives up raises the CTA's abort word; every later wait then fails
             // at once, the warps keep walking the loop for the barriers' sake, and the CTA
             // leaves together at the end of the piece without storing anything.
-            NMSPMM_PROF_T(tw);
             const bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(bars + s * 8, use & 1, abort_word));
-            NMSPMM_PROF_ADD(prof_wait, tw);
+            alive = alive && ok;
             if (live && ok) {
-                // HALF: the list holds columns of the merged 64-k window; the staged rows are
-                // its lower (even window) or upper (odd window) 32
-                const int half_base = Cfg::HALF ? (((win0 + w) & 1) << 5) : 0;
                 const uint32_t st = ring + s * Cfg::STAGE_BYTES;
                 const uint32_t as = st + a_rel, bs = st + b_rel;
 
-#ifndef NMSPMM_IDX_SHFL
-#define NMSPMM_IDX_SHFL 1
-#endif
-#ifndef NMSPMM_ASM_LDS
-#define NMSPMM_ASM_LDS 1
-#endif
-#if NMSPMM_IDX_SHFL
                 // Lane p resolves the window's p-th index of this warp's vector to a byte
                 // offset into As (HIGH: rank -> local column through the block's list); the
                 // offsets are handed round the warp by shuffle as the k loop needs them.
                 int my_off = 0;
                 if (lane < WS) {
                     int k = lds_s32(st + d_rel);
-                    if constexpr (MODE == kModeHigh) k = lds_s32(st + ci_rel + k * 4) - half_base;
+                    if constexpr (MODE == kModeHigh) k = lds_s32(st + ci_rel + k * 4);
                     if constexpr (Cfg::PAIR) k += (lane >= WS / 2) ? 32 : 0;       // second window of the pair
                     my_off = k * (MS * 4);
                 }
 #define NMSPMM_OFF(p) __shfl_sync(0xffffffffu, my_off, (p))
-#else
-                int row_off[WS];
-#pragma unroll
-                for (int p = 0; p < WS; ++p) row_off[p] = lds_s32(st + d_rel - (lane << (qs_shift + 2)) + ((p << qs_shift) << 2));
-                if constexpr (MODE == kModeHigh) {
-#pragma unroll
-                    for (int p = 0; p < WS; ++p) row_off[p] = lds_s32(st + ci_rel + row_off[p] * 4) - half_base;
-                }
-#pragma unroll
-                for (int p = 0; p < WS; ++p) row_off[p] = (row_off[p] + ((Cfg::PAIR && p >= WS / 2) ? 32 : 0)) * (MS * 4);
-#define NMSPMM_OFF(p) row_off[(p)]
-#endif
 
                 float a[2][MT];
                 float4 b[2][2];
                 auto load = [&](int p, int buf, int off) {
                     const uint32_t ap = as + off;
-#if NMSPMM_ASM_LDS
                     if constexpr (MT == 8) {
                         const float4 lo = lds_f4(ap), hi = lds_f4(ap + 32 * 4);
                         a[buf][0] = lo.x; a[buf][1] = lo.y; a[buf][2] = lo.z; a[buf][3] = lo.w;
@@ -275,20 +234,6 @@ __device__ __forceinline__ void nm_gemm_ffma_body(const GemmArgs& g, const CUten
                     const uint32_t bp = bs + p * (NS * 4);
                     b[buf][0] = lds_f4(bp);
                     b[buf][1] = lds_f4(bp + 16 * 4);
-#else
-                    const unsigned char* base = smem_raw - smem_u32(smem_raw);      // shared window origin
-                    if constexpr (MT == 8) {
-                        *reinterpret_cast<float4*>(&a[buf][0]) = *reinterpret_cast<const float4*>(base + ap);
-                        *reinterpret_cast<float4*>(&a[buf][4]) = *reinterpret_cast<const float4*>(base + ap + 32 * 4);
-                    } else if constexpr (MT == 4) {
-                        *reinterpret_cast<float4*>(&a[buf][0]) = *reinterpret_cast<const float4*>(base + ap);
-                    } else {
-                        *reinterpret_cast<float2*>(&a[buf][0]) = *reinterpret_cast<const float2*>(base + ap);
-                    }
-                    const uint32_t bp = bs + p * (NS * 4);
-                    b[buf][0] = *reinterpret_cast<const float4*>(base + bp);
-                    b[buf][1] = *reinterpret_cast<const float4*>(base + bp + 16 * 4);
-#endif
                 };
                 load(0, 0, NMSPMM_OFF(0));
                 int off_next = (WS > 1) ? NMSPMM_OFF(1) : 0;
@@ -331,7 +276,6 @@ __device__ __forceinline__ void nm_gemm_ffma_body(const GemmArgs& g, const CUten
         }
 
         // ---------------------------------------------------------------- end of the piece
-        NMSPMM_PROF_T(te);
         const int ty = tile / g.tiles_x, tx = tile - ty * g.tiles_x;
         const int bj = tx * NS, bi = ty * MS;
         const int col0 = bj + vec * kVecLen + (lane >> 4) * 8 + (lane & 1) * 4;      // and col0 + 16
@@ -416,20 +360,8 @@ __device__ __forceinline__ void nm_gemm_ffma_body(const GemmArgs& g, const CUten
             __syncthreads();                               // last_flag is reused by the next piece
         }
 
-        NMSPMM_PROF_ADD(prof_epi, te);
         cu += piece_n;                                     // on to the next piece of the range
     }
-#ifdef NMSPMM_PROFILE_WAITS
-    if (tid == 0) {
-        atomicAdd(&g_wait_profile[0], static_cast<unsigned long long>(prof_wait));
-        atomicAdd(&g_wait_profile[1], static_cast<unsigned long long>(prof_fill));
-        atomicAdd(&g_wait_profile[2], static_cast<unsigned long long>(clock64() - prof_start));
-        atomicAdd(&g_wait_profile[3], 1ull);
-        atomicAdd(&g_wait_profile[4], static_cast<unsigned long long>(prof_epi));
-        atomicMax(&g_wait_profile[5], static_cast<unsigned long long>(prof_epi));
-        atomicMax(&g_wait_profile[6], static_cast<unsigned long long>(clock64() - prof_start));
-    }
-#endif
 }
 
 // The two kernels: private C (the argument block of old), and C to several buffers.
@@ -472,7 +404,9 @@ cudaError_t launch_ffma(const GemmArgs& a, const GemmOutputs& outs, int grid, cu
     CUtensorMap map_a, map_b;
     e = encode_tensor_map_2d(&map_a, a.A, a.M, a.sched.n_win * Cfg::KS, MS, Cfg::KS);
     if (e != cudaSuccess) return e;
-    e = encode_tensor_map_2d(&map_b, a.B, a.N, a.W, NS, WS);
+    // (test hook: a box one row short delivers fewer bytes than the stage's barrier expects,
+    // so that the kernel's bounded waits run out; see nmspmm_test_short_fill)
+    e = encode_tensor_map_2d(&map_b, a.B, a.N, a.W, NS, WS - (g_test_short_fill ? 1 : 0));
     if (e != cudaSuccess) return e;
     if (MULTI)
         nm_gemm_ffma_multi_kernel<MS, NS, WM, WS, KS_, MODE><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(a, map_a, map_b, outs);

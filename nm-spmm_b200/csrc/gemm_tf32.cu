@@ -452,7 +452,7 @@ static cudaError_t launch_tf32(const GemmArgs& a, const GemmOutputs& outs, int t
     e = a_blocked ? encode_tensor_map_blocks32(&map_a, a.A, a.M, K, KW, 4)
                   : encode_tensor_map_2d(&map_a, a.A, a.M, K, 32, KW, 1);
     if (e != cudaSuccess) return e;
-    e = encode_tensor_map_blocks32(&map_b, a.B, a.N, a.W, Cfg::WSP, QT);
+    e = encode_tensor_map_blocks32(&map_b, a.B, a.N, a.W, Cfg::WSP - (g_test_short_fill ? 1 : 0), QT);   // (test hook, see kernels.h)
     if (e != cudaSuccess) return e;
     kernel<<<tiles, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(a, map_a, map_b, outs, a_blocked);
     return cudaGetLastError();

@@ -61,6 +61,10 @@ cudaError_t launch_reduce_pieces(int tile_id, const GemmArgs& args, const GemmOu
 cudaError_t launch_reduce_slices(int ns, const GemmArgs& args, const GemmOutputs& outs, int first_tile, int n_tiles,
                                  cudaStream_t st);
 
+// Test hook (nmspmm_test_short_fill): non-zero makes the multiply launchers encode B's tensor
+// map with a box one row short.  The kernels are unchanged; their stages then never fill.
+extern int g_test_short_fill;
+
 // packed = 0: scalar FFMA loop; 1: two-lane packed FFMA2 loop.
 cudaError_t measure_ffma_peak(double* tflops, int packed, cudaStream_t st);
 

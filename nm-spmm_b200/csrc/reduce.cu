@@ -67,6 +67,7 @@ nm_reduce_pieces_kernel(const GemmArgs g, const GemmOutputs outs, int first_tile
     const int tile = first_tile + blockIdx.x / MT, i = blockIdx.x % MT;
     const int tid = threadIdx.x;
     wait_for_the_multiply();
+    if (*reinterpret_cast<volatile int*>(g.status) != 0) return;      // a wait of the multiply gave up: the pieces are incomplete, leave C alone
     int v_first, v_last;
     tile_contributors(g.sched, tile, v_first, v_last);
     if (v_first == v_last) return;                         // one range held the whole tile and stored it
@@ -135,6 +136,7 @@ __global__ void __launch_bounds__(256) nm_reduce_slices_kernel(const GemmArgs g,
     const int bi = ty * MS, bj = tx * NS;
     const int S = g.sched.split_k;
     wait_for_the_multiply();
+    if (*reinterpret_cast<volatile int*>(g.status) != 0) return;      // a wait of the multiply gave up: the slices are incomplete, leave C alone
     const float4* slots = reinterpret_cast<const float4*>(g.partial) + static_cast<size_t>(sliced_tile) * S * (MS * V4);
     for (int e = threadIdx.x; e < ROWS * V4; e += 256) {
         const int row = r0 + e / V4, c4 = e % V4;

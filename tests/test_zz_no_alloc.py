@@ -45,6 +45,52 @@ def test_static_scratch_matches_caller_scratch_twice(pkg, M, N, K, n_keep, split
         assert torch.equal(got, want), "same kernel, same schedule: the sums are identical"
 
 
+def test_static_scratch_on_the_tensor_core_path_twice(pkg):
+    """The same two-calls-in-a-row check with K slices on the TF32 path (its slots are plain
+    row-major tiles added by the reduction kernel)."""
+    M, N, K, n_keep, split_k = 128, 512, 2048, 8, 4
+    p = pkg.formats.make_random(M, N, K, n_keep, seed=96)
+    op = pkg.NMSpMM.from_problem(p)
+    A = torch.from_numpy(p.A_km).cuda()
+    A2 = (torch.roll(A, 5, dims=1) * 0.5).contiguous()
+    desc = op.desc(M, path=pkg.PATH_TF32, split_k=split_k)
+    assert 0 < pkg.workspace_bytes(desc) <= pkg.STATIC_SCRATCH_BYTES
+    for a in (A, A2):
+        want = op.matmul(a, path=pkg.PATH_TF32, split_k=split_k)
+        got = torch.full((M, N), float("nan"), device="cuda")
+        pkg.gemm_static_scratch(desc, a, op.B, op.D, op.column_info, got)
+        torch.cuda.synchronize()
+        assert pkg.device_status() == 0
+        assert torch.equal(got, want), "same kernel, same slices, same order of addition"
+
+
+@pytest.mark.parametrize("M,path", [(64, 0), (256, 0), (512, 0), (64, 1)])
+def test_static_scratch_takes_shapes_whose_automatic_plan_is_too_big(pkg, M, path):
+    """An LLM-linear shape with the automatic schedule: nmspmm_gemm would want tens of MB of
+    slots here.  The no-allocation entry point must still run it (with a schedule that fits
+    its array), allocate nothing, and give the same product, twice in a row."""
+    N, K, n_keep = 11008, 4096, 8
+    p = pkg.formats.make_random(M, N, K, n_keep, seed=97)
+    op = pkg.NMSpMM.from_problem(p)
+    A = torch.from_numpy(p.A_km).cuda()
+    desc = op.desc(M, path=path)                        # split_k = 0: automatic
+    want = op.matmul(A, path=path)
+    tol = FP32_TOL if path == 0 else 2e-3               # another order of addition than `want`
+    got = torch.full((M, N), float("nan"), device="cuda")
+    pkg.gemm_static_scratch(desc, A, op.B, op.D, op.column_info, got)     # warm-up: resolves the array's address
+    torch.cuda.synchronize()
+    for _ in range(2):
+        got.fill_(float("nan"))
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()      # (nothing of torch's allocates between the two readings)
+        pkg.gemm_static_scratch(desc, A, op.B, op.D, op.column_info, got)
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        assert free_after == free_before, "the call must not take device memory"
+        assert pkg.device_status() == 0
+        assert _rel(got, want) <= tol
+
+
 def test_static_scratch_rejects_sizes_beyond_the_array(pkg):
     p = pkg.formats.make_random(128, 1024, 4096, 8, seed=95)
     op = pkg.NMSpMM.from_problem(p)
