@@ -18,6 +18,15 @@ no data-path collective.  Rank 0 prints one JSON line.
                     bounded row sample (N = 1, rank 0)
 * ``per_ratio``     the same step for 16:32, 12:32, 8:32, 4:32 (useful and
                     dense-equivalent TFLOP/s, roofline fraction)
+* ``tf32``          the tensor-core path on the same workload, every ratio
+* ``sustained``     the headline step launched back to back for a second, with the SM
+                    clock seen meanwhile (the K-step value is a burst)
+* ``parity``        sampled rows of every rank's result against the CPU checker, inside
+                    this run
+* ``workloads``     (N = 1) the other named configurations, both paths and the index
+                    packing alone, each against the slower of its HBM and FLOP time
+* ``large_sharded`` 8192 x 28672 x 8192, V = 64, split over the ranks (strong scaling),
+                    alone and with both all-gathers of C, each checked
 
 ``--impl reference`` times the reference's own CPU implementation of the path
 (oracle/_ref, compiled unchanged from the reference's sources; the C restatement
@@ -43,10 +52,7 @@ HEADLINE_KEEP = 8
 SETS = 3                      # operand sets rotated between steps (3 x 144 MB > 126 MB of L2)
 METRIC = "useful TFLOP/s, vector-wise N:M SpMM, 4096^3 8:32 V=32 FP32"
 
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the headline
-# kernel, from the ncu capture summarised in
-# profiles/nm_gemm_ffma_128x128_high_4096cubed_8of32.md.
-NCU_TRAFFIC_BYTES = {"nm_gemm_ffma_kernel<128,128,64,16,64,high> 4096^3 8:32": 127294976}
+SUSTAINED_SECONDS = 1.0       # back-to-back launches timed beside the K-step burst
 
 
 def algorithmic_bytes(M, N, K, n_keep, layout_ns=128):
@@ -135,6 +141,44 @@ def physical_gpu_index(local_rank: int) -> int:
     return local_rank
 
 
+def square_config(world: int) -> dict:
+    """The workload both arms are timed on (same keys, same values)."""
+    return {"workload": "square 4096^3, 8:32 (75 %), V=32, FP32 exact path", "M": M_SQ, "K": K_SQ,
+            "N_per_gpu": N_SQ, "N_total": N_SQ * world, "n_keep": HEADLINE_KEEP, "layout_ns": 128,
+            "parallelism": f"B column-vector groups sharded over {world} GPU(s), A replicated, no collective",
+            "l2": f"operands rotate over {SETS} sets of A and C (3 x 128 MB > 126 MB L2); no flush"}
+
+
+_checker = None
+
+
+def checker():
+    """The CPU checker (the C restatement of the reference's host multiply), all host threads."""
+    global _checker
+    if _checker is None:
+        import oracle
+        _checker = oracle.restatement()
+        try:
+            _checker.set_num_threads(len(os.sched_getaffinity(0)))
+        except Exception:
+            pass
+    return _checker
+
+
+def sampled_rows_error(A_km, BT, DT, n_keep, C_rows, rows, col0=0, f64=False):
+    """Relative Frobenius error of rows ``rows`` of a result (``C_rows``: those rows, columns
+    col0 .. col0 + BT.shape[1]) against the CPU checker on the same operands."""
+    K = A_km.shape[0]
+    w = np.arange(BT.shape[0], dtype=np.int32)[:, None]
+    B_col = np.ascontiguousarray(BT.T)
+    D_col = np.ascontiguousarray((DT + (w // n_keep) * 32).T.astype(np.int32))
+    sub = np.ascontiguousarray(A_km[:, rows])
+    with quiet_stdout():
+        want = (checker().nm_gemm_f64 if f64 else checker().nm_gemm_f32)(sub, B_col, D_col)
+    got = np.asarray(C_rows, dtype=np.float64)
+    return float(np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30))
+
+
 # ------------------------------------------------------------------------------------
 # CPU side: the reference's host multiply on a bounded sample.
 # ------------------------------------------------------------------------------------
@@ -202,8 +246,8 @@ def run_reference_arm(args, rank: int, world: int):
         "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded)",
-        "config": {"workload": "square 4096^3, 8:32, V=32, FP32 (reference's CPU multiply nmGEMM_on_cpu)",
-                   "M": M_SQ, "N": N_SQ, "K": K_SQ, "n_keep": HEADLINE_KEEP},
+        "config": square_config(world),
+        "timed": "the reference's CPU multiply nmGEMM_on_cpu on a bounded row sample of that workload",
         "cpu_baseline": {"value": value, "unit": "useful TFLOP/s", "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -285,12 +329,47 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     ms_per_step = ms / args.steps
     useful = 2.0 * M * n_local * p.W
     value = world * useful / (ms_per_step * 1e-3) / 1e12
+
+    def min_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return float(t.item())
+
+    def sustained(fn, flops_per_call):
+        """Back-to-back launches for about a second (events on the launching stream), with the
+        SM clock sampled meanwhile: what the K-step burst above turns into under load."""
+        smp = ClockSampler(physical_gpu_index(local_rank))
+        chunk, total_ms, calls = 100, 0.0, 0
+        with smp:
+            while total_ms < SUSTAINED_SECONDS * 1e3:
+                total_ms += time_steps(torch, fn, chunk)
+                calls += chunk
+        t = max_over_ranks(total_ms / calls)
+        return {"seconds": total_ms / 1e3, "launches": calls, "ms_per_step": t,
+                "value": world * flops_per_call / (t * 1e-3) / 1e12, "clocks": smp.summary()}
+
+    def parity_of(result, prob, rows, f64=False):
+        """Sampled rows of this rank's result against the CPU checker; worst rank wins."""
+        idx = torch.as_tensor(rows, device="cuda")
+        err = sampled_rows_error(prob.A_km, prob.BT, prob.DT, prob.n_keep, result[idx].cpu().numpy(), rows, f64=f64)
+        return err
+
+    # ---- parity inside this run: every rank checks rows of its own slab ---------------
+    check_rows = [0, 1, 127, 128, 1000, 2047, 2048, 4095]
+    err_here = parity_of(op.matmul(A_sets[0], path=path, tile=args.tile, split_k=args.split_k), p, check_rows,
+                         f64=(path == pkg.PATH_TF32))
+    tol_here = 1e-5 if path == pkg.PATH_FP32 else 2e-3
+    parity = {"rows_per_rank": len(check_rows), "max_rel_err": -min_over_ranks(-err_here), "tolerance": tol_here,
+              "checker": "C restatement of the reference's nmGEMM_on_cpu, on each rank's own operands"}
+    parity["ok"] = bool(parity["max_rel_err"] <= tol_here)
     if args.kernel_only:
         if rank == 0:
             print(json.dumps({"kernel_only": True, "ffma_peak": [pkg.measure_ffma_peak(False), pkg.measure_ffma_peak(True)],
                               "n_keep": keep, "path": args.path, "ms_per_step": ms_per_step, "useful_tflops": value,
                               "tile": [plan.tile_m, plan.tile_n], "split_k": plan.split_k, "grid": plan.grid, "stages": plan.stages,
-                              "clocks": sampler.summary()}), flush=True)
+                              "parity": parity, "clocks": sampler.summary()}), flush=True)
         if world > 1:
             dist.destroy_process_group()
         return
@@ -312,7 +391,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     roofline = {
         "bound": "fp32_simt" if t_flop >= t_mem else "hbm",
         "achieved": achieved, "peak": ffma_peak, "unit": "TFLOP/s", "frac": max(t_flop, t_mem) / (ms_per_step * 1e-3),
-        "traffic": NCU_TRAFFIC_BYTES.get("nm_gemm_ffma_kernel<128,128,64,16,64,high> 4096^3 8:32"),
+        "traffic": None,
+        "traffic_source": "not measured in this run (DRAM counters need ncu); one capture of this kernel and workload is "
+                          "summarised in profiles/nm_gemm_ffma_128x128_high_4096cubed_8of32.md",
         "peak_source": "FP32 FMA rate measured live on this GPU by the library's register-only kernels, larger of "
                        f"scalar FFMA ({ffma_scalar:.1f}) and packed FFMA2 ({ffma_packed:.1f} TFLOP/s); "
                        "nominal 148 SMs x 128 lanes x 2 x SM clock",
@@ -324,6 +405,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                   f"{plan.stages} stages, {plan.smem_bytes} B smem",
         "kernel_ms": ms_per_step,
     }
+
+    sustained_fp32 = sustained(step, useful)
 
     # ---- the other ratios (N=1 only, short) ---------------------------------------
     per_ratio = []
@@ -346,7 +429,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if world == 1:
         tf32_peak = float(peaks.get("bf16_tflops", 1590.0)) / 2.0      # dense TF32 = half the dense bf16 rate
         rows = []
-        for n_keep in (16, 8, 4):
+        tf32_sustained = None
+        for n_keep in (16, 12, 8, 4):
             pr = p if n_keep == HEADLINE_KEEP else pkg.formats.make_random(M, n_local, K, n_keep, seed=0)
             opr = op if n_keep == HEADLINE_KEEP else pkg.NMSpMM.from_problem(pr, layout_ns=128)
             fn = lambda i, o=opr: o.matmul(A_sets[i % SETS], out=C_sets[i % SETS], path=pkg.PATH_TF32)
@@ -355,14 +439,20 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             t = time_steps(torch, fn, 20) / 20
             uf = 2.0 * M * n_local * pr.W
             tf, tm = uf / (tf32_peak * 1e12), algorithmic_bytes(M, n_local, K, n_keep) / (hbm_gbs * 1e9)
+            got = opr.matmul(A_sets[0], path=pkg.PATH_TF32)
             exact = opr.matmul(A_sets[0])
-            err = float((opr.matmul(A_sets[0], path=pkg.PATH_TF32) - exact).norm() / exact.norm())
+            err = float((got - exact).norm() / exact.norm())
+            err64 = parity_of(got, pr, check_rows, f64=True)
             info = pkg.plan(opr.desc(M, path=pkg.PATH_TF32))
             rows.append({"n_keep": n_keep, "path": "tf32", "ms": t, "useful_tflops": uf / (t * 1e-3) / 1e12,
                          "dense_equivalent_tflops": 2.0 * M * n_local * K / (t * 1e-3) / 1e12,
                          "roofline_frac": max(tf, tm) / (t * 1e-3), "rel_err_vs_fp32_path": err,
-                         "tile": [info.tile_m, info.tile_n]})
-        tf32 = {"kernel": "nm_gemm_tf32_kernel, tcgen05.mma kind::tf32 M128 N32 K8, A gathered into TMEM per vector",
+                         "rel_err_vs_fp64_checker_rows": err64, "tile": [info.tile_m, info.tile_n]})
+            if n_keep == HEADLINE_KEEP:
+                tf32_sustained = sustained(fn, uf)
+        tf32 = {"kernel": "nm_gemm_tf32_kernel: per k window one tcgen05.mma kind::tf32 chain gathers the selected columns "
+                          "of A into TMEM (A window x one-hot matrix, M128 N<=128), then M128 N32 K8 products per vector",
+                "sustained_8of32": tf32_sustained,
                 "bound": "tensor", "peak": tf32_peak, "unit": "TFLOP/s",
                 "peak_source": "half of the measured dense bf16 rate in MEASURED_PEAKS.json (burst)"
                                if "bf16_tflops" in peaks else "half of the fallback 1590 TFLOP/s bf16",
@@ -370,11 +460,30 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                 "per_ratio": rows}
 
     # ---- end to end through the host-buffer entry point ------------------------------
-    hA = torch.from_numpy(p.A_km).pin_memory()
-    hB = torch.from_numpy(p.BT).pin_memory()
-    hD = torch.from_numpy(p.DT).pin_memory()
+    # Every rank pins its buffers on the NUMA node of its own GPU (first touch by a process
+    # bound there): with eight ranks copying at once, buffers on the far socket would put the
+    # inter-socket link between every GPU and its data.
+    saved_affinity = os.sched_getaffinity(0)
+    numa_bound = pkg.bind_host_to_gpu(local_rank)
+    hA = torch.empty(p.A_km.shape, dtype=torch.float32).pin_memory().copy_(torch.from_numpy(p.A_km))
+    hB = torch.empty(p.BT.shape, dtype=torch.float32).pin_memory().copy_(torch.from_numpy(p.BT))
+    hD = torch.empty(p.DT.shape, dtype=torch.int32).pin_memory().copy_(torch.from_numpy(p.DT))
     hC = torch.empty((M, n_local), dtype=torch.float32).pin_memory()
+    hC.zero_()
     e2e_steps = max(3, min(args.steps, 10))
+
+    def link_gbs(dst, src):
+        """One direction of this rank's host link alone: a plain copy of one buffer, all ranks at once."""
+        dst.copy_(src, non_blocking=True)
+        torch.cuda.synchronize()
+        ms = time_steps(torch, lambda i: dst.copy_(src, non_blocking=True), 3, barrier) / 3
+        return src.numel() * 4 / (ms * 1e-3) / 1e9
+
+    link = {"h2d_gbs_min_over_ranks": min_over_ranks(link_gbs(A_sets[0], hA)),
+            "d2h_gbs_min_over_ranks": min_over_ranks(link_gbs(hC, C_sets[0])),
+            "numa_bound": bool(numa_bound),
+            "note": "a 64 MiB pinned buffer copied alone, every rank at the same time; the e2e call moves "
+                    "%.0f MB in and %.0f MB out per step" % ((hA.numel() + hB.numel() + hD.numel()) * 4 / 1e6, hC.numel() * 4 / 1e6)}
 
     def e2e_step(i):
         pkg.gemm_host(desc, hA, hB, hD, hC, on_current_stream=True)
@@ -384,8 +493,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     e2e_ms = max_over_ranks(time_steps(torch, e2e_step, e2e_steps, barrier)) / e2e_steps
     h2d = hA.numel() * 4 + hB.numel() * 4 + hD.numel() * 4
     d2h = hC.numel() * 4
+    os.sched_setaffinity(0, saved_affinity)
     e2e = {"value": world * useful / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps, "host_link": link,
+           "copy_time_floor_ms": max(h2d / (link["h2d_gbs_min_over_ranks"] * 1e6), d2h / (link["d2h_gbs_min_over_ranks"] * 1e6)),
            "call": "nmspmm_gemm_host (pinned host A, B, raw indices -> packed on the GPU -> multiply -> host C)"}
     # parity of what the e2e call returned, against the resident-operand result
     e2e_err = float((hC.cuda() - C_sets[0].copy_(op.matmul(A_sets[0]))).norm() / C_sets[0].norm())
@@ -400,16 +511,33 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     torch.cuda.empty_cache()
     LM, LN, LK, LKEEP = WORKLOADS["large"][:4]
     pl = pkg.formats.make_random(LM, LN, LK, LKEEP, seed=0, vec_len=64)
-    sh = pkg.sharding.ShardedNMSpMM(pkg, pl.BT, pl.DT, LK, LKEEP, rank, world)
+    sh = pkg.sharding.ShardedNMSpMM(pkg, pl.BT, pl.DT, LK, LKEEP, rank, world, vec_len=64)
     LA = torch.from_numpy(pl.A_km).cuda()
     l_useful = pl.useful_flops()
     l_steps = 5
+    c0, c1 = sh.columns
     large = {"workload": "8192 x 28672 x 8192, 8:32, V=64, column-vector groups over %d GPU(s)" % world,
              "scaling": "strong", "columns_of_rank0": list(sh.columns), "steps": l_steps}
-    modes = [("multiply", False)] + ([("multiply_then_nccl_all_gather", True), ("multiply_with_fused_all_gather", "fused")]
-                                     if world > 1 else [])
-    for name, gather in modes:
-        fn = lambda i, g=gather: sh.matmul(LA, gather=g)
+    slab_rows = [int(r) for r in np.linspace(0, LM - 1, 64).astype(np.int64)]      # 64 rows of every rank's slab
+    full_rows = [0, 4095, 8191, 127, 128, 6000, 2049, 7777]                       # rows of the gathered C, rank 0
+
+    def slab_error(C, f64=False):
+        """This rank's columns of rows ``slab_rows`` against the CPU checker on this rank's slab of B."""
+        idx = torch.as_tensor(slab_rows, device="cuda")
+        cols = C[idx][:, c0:c1] if C.shape[1] == LN else C[idx]
+        return sampled_rows_error(pl.A_km, pl.BT[:, c0:c1], pl.DT[:, c0 // 32:c1 // 32], LKEEP, cols.cpu().numpy(),
+                                  slab_rows, f64=f64)
+
+    def all_ranks_ok(flag: bool) -> bool:
+        return min_over_ranks(1.0 if flag else 0.0) == 1.0
+
+    modes = [("multiply", False, pkg.PATH_FP32), ("multiply_tf32", False, pkg.PATH_TF32)]
+    if world > 1:
+        modes += [("multiply_then_nccl_all_gather", True, pkg.PATH_FP32), ("multiply_with_fused_all_gather", "fused", pkg.PATH_FP32),
+                  ("multiply_tf32_with_fused_all_gather", "fused", pkg.PATH_TF32)]
+    gathered = {}
+    for name, gather, lpath in modes:
+        fn = lambda i, g=gather, pa=lpath: sh.matmul(LA, gather=g, path=pa)
         # the gathers are optional extras of the path: a set-up failure on one rank (peer
         # mapping, NCCL) must not take the headline line down, and every rank must agree
         # on whether the mode runs at all
@@ -421,17 +549,49 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         except Exception as exc:      # noqa: BLE001
             ok, why = 0.0, f"{type(exc).__name__}: {exc}"[:200]
         if world > 1:
-            flag = torch.tensor([ok], dtype=torch.float64, device="cuda")
-            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-            if float(flag.item()) == 0.0:
+            if min_over_ranks(ok) == 0.0:
                 large[name] = {"unavailable": why if ok == 0.0 else "failed on another rank"}
                 continue
         elif ok == 0.0:
             raise RuntimeError(why)
         t = max_over_ranks(time_steps(torch, fn, l_steps, barrier)) / l_steps
-        large[name] = {"ms": t, "useful_tflops": l_useful / (t * 1e-3) / 1e12}
+        # ---- the result of this mode, checked on every rank --------------------------------
+        C = fn(0)
+        torch.cuda.synchronize()
+        barrier()
+        is_tf32 = lpath == pkg.PATH_TF32
+        tol = 2e-3 if is_tf32 else 1e-5
+        err = slab_error(C, f64=is_tf32)
+        entry = {"ms": t, "useful_tflops": l_useful / (t * 1e-3) / 1e12,
+                 "slab_rel_err_max_over_ranks": -min_over_ranks(-err), "tolerance": tol, "rows_checked_per_rank": len(slab_rows)}
+        good = err <= tol
+        if gather:
+            # every rank holds the full C: rank 0 checks rows across all slabs against the checker,
+            # and the two gathers of the same path must agree bit for bit on every rank
+            if rank == 0:
+                idx = torch.as_tensor(full_rows, device="cuda")
+                e_full = sampled_rows_error(pl.A_km, pl.BT, pl.DT, LKEEP, C[idx].cpu().numpy(), full_rows, f64=is_tf32)
+                entry["gathered_rel_err_rank0"] = e_full
+                good = good and e_full <= tol
+            key = "tf32" if is_tf32 else "fp32"
+            if key in gathered:
+                same = bool(torch.equal(C, gathered[key]))
+                entry["equals_nccl_gather_on_every_rank"] = all_ranks_ok(same)
+                good = good and same
+            else:
+                gathered[key] = C.clone()
+        entry["parity"] = all_ranks_ok(bool(good))
+        large[name] = entry
+    gathered.clear()
     if pkg.device_status() != 0:
         raise RuntimeError("a device-side bounded wait gave up in the large sharded configuration")
+    del LA, sh
+    torch.cuda.empty_cache()
+
+    # ---- the other named configurations (N = 1) ------------------------------------------
+    workloads = None
+    if world == 1:
+        workloads = {name: measure_workload(pkg, torch, name, 0, 0, quick=True) for name in ("llm16", "llm64", "llm256", "deepk")}
 
     if rank == 0:
         line = {
@@ -439,14 +599,11 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded splitmix64: A, kept values U[-1,1), "
                                                        "random sorted indices)",
-            "config": {"workload": "square 4096^3, 8:32 (75 %), V=32, FP32 exact path", "M": M, "K": K,
-                       "N_per_gpu": n_local, "N_total": n_local * world, "n_keep": HEADLINE_KEEP, "layout_ns": 128,
-                       "parallelism": f"B column-vector groups sharded over {world} GPU(s), A replicated, no collective",
-                       "l2": f"operands rotate over {SETS} sets of A and C (3 x 128 MB > 126 MB L2); no flush"},
+            "config": square_config(world),
             "dense_equivalent_tflops": world * 2.0 * M * n_local * K / (ms_per_step * 1e-3) / 1e12,
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "e2e_rel_err_vs_resident": e2e_err,
-            "gpu_launches": args.steps, "clocks": sampler.summary(), "per_ratio": per_ratio, "tf32": tf32,
-            "large_sharded": large,
+            "gpu_launches": args.steps, "clocks": sampler.summary(), "parity": parity, "sustained": sustained_fp32,
+            "per_ratio": per_ratio, "tf32": tf32, "large_sharded": large, "workloads": workloads,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -460,17 +617,13 @@ WORKLOADS = {
 }
 
 
-def run_workload(args):
-    """One of the other named configurations on one GPU: per-launch device time with the L2
-    flushed between launches (these shapes are small enough to live in L2 otherwise), the
-    index packing timed alone, and the roofline fraction of each path."""
-    import torch
-
-    from __graft_entry__ import load_package
-    pkg = load_package(native=True)
-    torch.cuda.set_device(0)
-    M, N, K, n_keep, vec = WORKLOADS[args.workload]
-    p = pkg.formats.make_random(M, N, K, n_keep, seed=0, vec_len=vec, a_dist="normal" if args.workload.startswith("llm") else "uniform")
+def measure_workload(pkg, torch, name: str, tile: int = 0, split_k: int = 0, steps: int = 50, quick: bool = False) -> dict:
+    """One of the other named configurations on one GPU: per-launch device time with the
+    operands cycled so that no launch finds them in L2 (these shapes are small enough to live
+    there otherwise), the index packing timed alone, the roofline fraction of each path, and
+    the result of each path checked against the CPU checker."""
+    M, N, K, n_keep, vec = WORKLOADS[name]
+    p = pkg.formats.make_random(M, N, K, n_keep, seed=0, vec_len=vec, a_dist="normal" if name.startswith("llm") else "uniform")
     raw = torch.from_numpy(p.DT).cuda()
     useful, abytes = p.useful_flops(), algorithmic_bytes(M, N, K, n_keep)
     # Replicas of the sparse operand and of C, cycled launch after launch, so that a launch
@@ -478,7 +631,7 @@ def run_workload(args):
     # that the device time is not padded by host launch latency (some of these kernels take
     # tens of microseconds).
     n_rep = max(2, min(8, -(-(300 << 20) // abytes)))
-    reps = n_rep * max(2, args.steps // n_rep)
+    reps = n_rep * max(2, (16 if quick else steps) // n_rep)
 
     def graph_time(fns):
         for f in fns:
@@ -518,21 +671,34 @@ def run_workload(args):
     fp32_peak = max(pkg.measure_ffma_peak(False), pkg.measure_ffma_peak(True)) * 1e12
     tf32_peak = float(peaks.get("bf16_tflops", 1590.0)) / 2.0 * 1e12
     pack_bytes = 2 * raw.numel() * 4 + (outs[0][1].numel() * 4 if isinstance(outs[0], tuple) else 0)
-    out = {"workload": args.workload, "M": M, "N": N, "K": K, "n_keep": n_keep, "vec_len": vec,
+    out = {"workload": name, "M": M, "N": N, "K": K, "n_keep": n_keep, "vec_len": vec,
            "index_packing_ms": pack_ms, "index_packing_gbs": pack_bytes / (pack_ms * 1e-3) / 1e9,
            "algorithmic_bytes": abytes, "useful_flops": useful, "hbm_time_us": abytes / hbm * 1e6,
            "l2": f"{n_rep} replicas of B, indices and C cycled (working set {n_rep * abytes >> 20} MB); "
                  f"{reps} launches replayed from a CUDA graph"}
-    for name, path, peak in (("fp32", pkg.PATH_FP32, fp32_peak), ("tf32", pkg.PATH_TF32, tf32_peak)):
-        fns = [lambda o=o, c=c: o.matmul(A, out=c, path=path, tile=args.tile, split_k=args.split_k) for o, c in zip(ops, Cs)]
+    rows = sorted(set(int(r) for r in np.linspace(0, M - 1, min(M, 16)).astype(np.int64)))
+    for pname, path, peak in (("fp32", pkg.PATH_FP32, fp32_peak), ("tf32", pkg.PATH_TF32, tf32_peak)):
+        fns = [lambda o=o, c=c: o.matmul(A, out=c, path=path, tile=tile, split_k=split_k) for o, c in zip(ops, Cs)]
         ms = graph_time(fns)
-        plan = pkg.plan(ops[0].desc(M, path=path, tile=args.tile, split_k=args.split_k))
-        out[name] = {"ms": ms, "useful_tflops": useful / (ms * 1e-3) / 1e12, "bytes_per_s_gbs": abytes / (ms * 1e-3) / 1e9,
-                     "roofline_frac": max(useful / peak, abytes / hbm) / (ms * 1e-3),
-                     "bound": "hbm" if abytes / hbm > useful / peak else "flops",
-                     "tile": [plan.tile_m, plan.tile_n], "ctas": plan.grid, "whole_tiles": plan.n_dp}
+        plan = pkg.plan(ops[0].desc(M, path=path, tile=tile, split_k=split_k))
+        err = sampled_rows_error(p.A_km, p.BT, p.DT, n_keep, Cs[0][torch.as_tensor(rows, device="cuda")].cpu().numpy(), rows,
+                                 f64=(pname == "tf32"))
+        out[pname] = {"ms": ms, "useful_tflops": useful / (ms * 1e-3) / 1e12, "bytes_per_s_gbs": abytes / (ms * 1e-3) / 1e9,
+                      "roofline_frac": max(useful / peak, abytes / hbm) / (ms * 1e-3),
+                      "bound": "hbm" if abytes / hbm > useful / peak else "flops",
+                      "tile": [plan.tile_m, plan.tile_n], "ctas": plan.grid, "whole_tiles": plan.n_dp,
+                      "rel_err_rows": err, "parity": bool(err <= (1e-5 if pname == "fp32" else 2e-3))}
     assert pkg.device_status() == 0
-    print(json.dumps(out), flush=True)
+    return out
+
+
+def run_workload(args):
+    import torch
+
+    from __graft_entry__ import load_package
+    pkg = load_package(native=True)
+    torch.cuda.set_device(0)
+    print(json.dumps(measure_workload(pkg, torch, args.workload, args.tile, args.split_k, args.steps)), flush=True)
 
 
 def main():

@@ -345,6 +345,39 @@ def gemm_host(desc: GemmDesc, A_km, BT, DT, C, on_current_stream: bool = False) 
     _check("nmspmm_gemm_host", lib.nmspmm_gemm_host(ctypes.byref(desc), ptr(A_km), ptr(BT), ptr(DT), ptr(C), st))
 
 
+def gpu_numa_cpus(device_index: int):
+    """CPUs of the NUMA node the GPU hangs off (from sysfs), or None when that cannot be read
+    (single-node hosts report node -1)."""
+    try:
+        pr = _torch().cuda.get_device_properties(device_index)
+        bdf = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        node = int(open(f"/sys/bus/pci/devices/{bdf}/numa_node").read())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        return cpus or None
+    except Exception:
+        return None
+
+
+def bind_host_to_gpu(device_index: int) -> bool:
+    """Pins the calling process to the CPUs next to the GPU, so that pinned host buffers
+    allocated afterwards (first touch) and the copies that read them stay on that NUMA node:
+    what the host-buffer entry point wants when every GPU of a box runs one.  Returns whether
+    anything was changed; os.sched_setaffinity(0, saved) undoes it."""
+    cpus = gpu_numa_cpus(device_index)
+    if not cpus:
+        return False
+    allowed = os.sched_getaffinity(0) & cpus
+    if not allowed:
+        return False
+    os.sched_setaffinity(0, allowed)
+    return True
+
+
 def measure_ffma_peak(packed: bool = False) -> float:
     """Sustained FP32 FMA rate of the current GPU in TFLOP/s (register-only kernel);
     ``packed`` selects the two-lane packed FMA of sm_100 instead of scalar FFMA."""

@@ -4,8 +4,7 @@ The column vectors of B are independent, so C = A.B splits by columns with no
 exchange: rank r owns a contiguous group of whole index blocks (``layout_ns``
 columns each), the matching slab of compressed values and indices, and produces
 the column slab ``C[:, c0:c1]``.  A is replicated.  The only collective is the
-optional all-gather of C.  (The reference has no multi-GPU path; this is the
-partition BASELINE's sharded configuration asks for.)
+optional all-gather of C.  (The reference has no multi-GPU path.)
 """
 from __future__ import annotations
 
@@ -63,10 +62,10 @@ class ShardedNMSpMM:
     """The rank-local part of a column-sharded sparse operand (one process per GPU)."""
 
     def __init__(self, pkg, BT: np.ndarray, DT: np.ndarray, K: int, n_keep: int, rank: int, world: int,
-                 layout_ns: int = 128, device=None):
+                 layout_ns: int = 128, device=None, vec_len: int = 32):
         self.N, self.world, self.rank, self.layout_ns = BT.shape[1], world, rank, layout_ns
         bt, dt, self.columns = shard_operands(BT, DT, rank, world, layout_ns)
-        self.local = pkg.NMSpMM(bt, dt, K, n_keep, layout_ns, device=device)
+        self.local = pkg.NMSpMM(bt, dt, K, n_keep, layout_ns, device=device, vec_len=vec_len)
         self._symm = None
 
     def matmul(self, A, gather=False, **kw):
