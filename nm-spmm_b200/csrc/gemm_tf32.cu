@@ -94,12 +94,12 @@ struct Tf32Cfg {
     static constexpr int ST0 = (SMEM_LIMIT - 1024 - AUX_BYTES - CTRL_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = ST0 > 6 ? 6 : ST0;
     static_assert(STAGES >= 2, "at least two stages");
-    // Ring of gather results beside the accumulators.  The gather of step t waits for the
-    // products of step t - NBUF through that step's stage barrier, whose phase must still be
-    // the current one: NBUF < STAGES.
+    // Ring of gather results beside the accumulators.  A gather's result is complete (and its
+    // commit arrives) some hundreds of cycles after issue, and the products that free the
+    // buffer again take as long: the loop gather -> products -> gather is latency-bound
+    // unless several steps are in flight, so the ring is as deep as Tensor Memory allows.
     static constexpr int NBUF0 = DIRECT ? 1 : (TMEM_COLS - NS) / N1;
-    static constexpr int NBUF1 = NBUF0 > 3 ? 3 : NBUF0;
-    static constexpr int NBUF = NBUF1 >= STAGES ? STAGES - 1 : NBUF1;
+    static constexpr int NBUF = NBUF0 > 4 ? 4 : NBUF0;
     static_assert(NBUF >= 1, "no room for a gather result beside the accumulators");
     static constexpr int EPI_BYTES = 4 * 32 * 144;           // four warps' 32 x 32 transposition patches, rows 144 bytes apart
     static_assert(EPI_BYTES <= STAGES * STAGE_BYTES, "the epilogue reuses the stage ring");
@@ -134,9 +134,9 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
     const uint32_t prev_k = k_ring + RING * 512;                          // [STAGES][128] one-hot entry now set in the stage
     const uint32_t bars = ring + STAGES * Cfg::STAGE_BYTES + Cfg::AUX_BYTES;
     const uint32_t bar_full = bars, bar_empty = bars + STAGES * 8;
-    const uint32_t bar_gdone = bar_empty + STAGES * 8, bar_acc = bar_gdone + 3 * 8;
+    const uint32_t bar_gdone = bar_empty + STAGES * 8, bar_gfree = bar_gdone + 4 * 8, bar_acc = bar_gfree + 4 * 8;
     const uint32_t tmem_word = bar_acc + 8, abort_word = tmem_word + 4;
-    static_assert((2 * 6 + 3 + 1) * 8 + 8 <= Cfg::CTRL_BYTES, "control block");
+    static_assert((2 * 6 + 2 * 4 + 1) * 8 + 8 <= Cfg::CTRL_BYTES, "control block");
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // The first n_dp CTAs take one whole tile each.  The remaining tiles (the partial last
@@ -159,7 +159,10 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
             mbar_init(bar_full + s * 8, DIRECT ? 1 : 1 + Cfg::BUILDERS / 32);   // the TMA bytes + the builder warps
             mbar_init(bar_empty + s * 8, DIRECT ? 1 : Cfg::PRODUCT_WARPS);      // the commits behind the step's products
         }
-        for (int b = 0; b < 3; ++b) mbar_init(bar_gdone + b * 8, 1);
+        for (int b = 0; b < 4; ++b) {
+            mbar_init(bar_gdone + b * 8, 1);                                    // the commit behind a gather
+            mbar_init(bar_gfree + b * 8, Cfg::PRODUCT_WARPS);                   // the commits behind the products that read it
+        }
         mbar_init(bar_acc, DIRECT ? 1 : Cfg::PRODUCT_WARPS);
         sts_volatile_s32(abort_word, 0);
         mbar_init_fence();
@@ -221,10 +224,8 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
             bool ok = mbar_wait_bounded(bar_full + s * 8, (t / STAGES) & 1, abort_word);
             TF_ADD(m_full, t0);
             TF_T(t1);
-            if (!DIRECT && t >= NBUF) {                    // the result buffer is free once the products of step t - NBUF are done
-                const int u = t - NBUF;
-                ok = ok && mbar_wait_bounded(bar_empty + (u % STAGES) * 8, (u / STAGES) & 1, abort_word);
-            }
+            if (!DIRECT && t >= NBUF)                      // the result buffer is free once the products of step t - NBUF are done
+                ok = ok && mbar_wait_bounded(bar_gfree + (t % NBUF) * 8, ((t / NBUF) - 1) & 1, abort_word);
             TF_ADD(m_free, t1);
             if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
             TF_T(t2);
@@ -240,12 +241,8 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
                     tc_commit(bar_empty + s * 8);
                 } else {
                     const uint32_t gbuf = tmem_addr(tmem, 0, Cfg::ACOL0 + (t % NBUF) * Cfg::N1);
-#ifdef NMSPMM_TF32_SKIP_G
-                    for (int ks = 0; ks < 1; ++ks)
-#else
 #pragma unroll
                     for (int ks = 0; ks < Cfg::NKS; ++ks)
-#endif
                         umma_tf32_ss(gbuf, umma_desc_mn_tf32(st + ks * 1024, KW * 128, 512),
                                      umma_desc_mn_tf32(st + Cfg::A_BYTES + Cfg::B_BYTES + ks * 1024, KW * 128, 512),
                                      idesc_gather, ks != 0);
@@ -288,20 +285,18 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
                     if (v_begin < v_end) {
                         const uint32_t bs = ring + s * Cfg::STAGE_BYTES + Cfg::A_BYTES;
                         const uint32_t gbuf = tmem_addr(tmem, 0, Cfg::ACOL0 + b * Cfg::N1);
-#ifdef NMSPMM_TF32_SKIP_C
-                        for (int v = v_begin; v < v_begin + 1; ++v) {
-#else
                         for (int v = v_begin; v < v_end; ++v) {
-#endif
 #pragma unroll
                             for (int gi = 0; gi < Cfg::G; ++gi)
                                 umma_tf32_ts(tmem_addr(tmem, 0, v * VL), gbuf + v * WSP + gi * 8,
                                              umma_desc_mn_tf32(bs + v * (BPV * WSP * 128) + gi * 1024, WSP * 128, 512),
                                              idesc_product, (u | gi) != 0);
                         }
-                        tc_commit(bar_empty + s * 8);      // this half of the step's products has read the stage and the gather result
+                        tc_commit(bar_empty + s * 8);      // this half of the step's products has read the stage
+                        tc_commit(bar_gfree + b * 8);      // and the gather result
                     } else {
                         mbar_arrive(bar_empty + s * 8);    // no vector of this half exists; the gather itself has completed
+                        mbar_arrive(bar_gfree + b * 8);
                     }
                 }
                 __syncwarp();
