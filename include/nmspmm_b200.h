@@ -139,6 +139,17 @@ int nmspmm_gemm(const nmspmm_gemm_desc* desc,
                 const float* A_dev, const float* B_dev, const int* D_dev, const int* column_info_dev,
                 float* C_dev, void* workspace_dev, size_t workspace_bytes, void* stream);
 
+/* The multiply for activations stored row-major, A[i*K + k] (no counterpart in the reference,
+ * whose A is col-major, include/utils.h:34-38; a linear layer's input is not).  A first kernel
+ * on `stream` writes the col-major copy (its k rows padded to a multiple of 4 floats, so M
+ * may be any positive number here) into the head of the workspace, the multiply follows.
+ * C is row-major M x N as everywhere.  The workspace holds that copy and then what
+ * nmspmm_gemm needs: ask nmspmm_gemm_row_major_workspace_bytes. */
+size_t nmspmm_gemm_row_major_workspace_bytes(const nmspmm_gemm_desc* desc);
+int nmspmm_gemm_row_major(const nmspmm_gemm_desc* desc,
+                          const float* A_rows_dev, const float* B_dev, const int* D_dev, const int* column_info_dev,
+                          float* C_dev, void* workspace_dev, size_t workspace_bytes, void* stream);
+
 /* The multiply of one rank of a column-sharded B fused with the all-gather of C (no
  * counterpart in the reference, which runs on one GPU).  The rank's problem is
  * desc (N = the columns of its slab); every finished tile is stored, inside the multiply

@@ -34,7 +34,8 @@ C_ABI_SYMBOLS = (
     "nmspmm_status_string", "nmspmm_last_cuda_error", "nmspmm_version",
     "nmspmm_trans_index_device", "nmspmm_preprocess_low_device", "nmspmm_preprocess_high_device",
     "nmspmm_trans_index_host", "nmspmm_preprocess_low_host", "nmspmm_preprocess_high_host",
-    "nmspmm_test_short_fill", "nmspmm_gemm_workspace_bytes", "nmspmm_gemm", "nmspmm_gemm_with_cached_workspace", "nmspmm_device_status",
+    "nmspmm_test_short_fill", "nmspmm_gemm_workspace_bytes", "nmspmm_gemm", "nmspmm_gemm_row_major",
+    "nmspmm_gemm_row_major_workspace_bytes", "nmspmm_gemm_with_cached_workspace", "nmspmm_device_status",
     "nmspmm_gemm_plan", "nmspmm_gemm_host", "nmspmm_release_cached", "nmspmm_measure_ffma_peak",
     "nmspmm_gemm_static_scratch", "nmspmm_gemm_gather", "nmspmm_prune_device",
 )
@@ -87,6 +88,9 @@ def load_library():
     lib.nmspmm_gemm_workspace_bytes.restype = sz
     lib.nmspmm_gemm_workspace_bytes.argtypes = [ctypes.POINTER(GemmDesc)]
     lib.nmspmm_gemm.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp, vp, sz, vp]
+    lib.nmspmm_gemm_row_major_workspace_bytes.restype = sz
+    lib.nmspmm_gemm_row_major_workspace_bytes.argtypes = [ctypes.POINTER(GemmDesc)]
+    lib.nmspmm_gemm_row_major.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp, vp, sz, vp]
     lib.nmspmm_gemm_with_cached_workspace.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp, vp]
     lib.nmspmm_gemm_static_scratch.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp, vp]
     lib.nmspmm_prune_device.argtypes = [vp, vp, vp, ci, ci, ci, ci, vp]
@@ -441,6 +445,25 @@ class NMSpMM:
         d = self.desc(M, path, split_k, tile)
         C = torch.empty((M, self.N), dtype=torch.float32, device=A.device) if out is None else out
         gemm(d, A, self.B, self.D, self.column_info, C, self._scratch(workspace_bytes(d)))
+        return C
+
+    def matmul_rows(self, x, path: int = PATH_FP32, split_k: int = 0, tile: int = 0, out=None):
+        """C (M, N) = x . B for ``x`` given row-major as an (M, K) float32 CUDA tensor (any M >= 1):
+        the library transposes on the GPU ahead of the multiply (nmspmm_gemm_row_major)."""
+        torch = _torch()
+        M, K = x.shape
+        assert K == self.K and x.is_contiguous() and x.dtype == torch.float32
+        d = self.desc(M, path, split_k, tile)
+        need = int(load_library().nmspmm_gemm_row_major_workspace_bytes(ctypes.byref(d)))
+        if need == 0:
+            raise NMSpMMError("nmspmm_gemm_row_major_workspace_bytes", UNSUPPORTED)
+        ws = self._scratch(need)
+        C = torch.empty((M, self.N), dtype=torch.float32, device=x.device) if out is None else out
+        col = ctypes.c_void_p(self.column_info.data_ptr()) if self.column_info is not None else ctypes.c_void_p(0)
+        _check("nmspmm_gemm_row_major",
+               load_library().nmspmm_gemm_row_major(ctypes.byref(d), ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(self.B.data_ptr()),
+                                                   ctypes.c_void_p(self.D.data_ptr()), col, ctypes.c_void_p(C.data_ptr()),
+                                                   ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr()))
         return C
 
     def matmul_into(self, A, out_ptrs, ldc: int, col0: int, path: int = PATH_FP32, split_k: int = 0, tile: int = 0) -> None:

@@ -98,11 +98,13 @@ struct Plan {
 // of a 128 x 128 tile); the kernel spreads that over the GPU for one launch (2-3 us).
 constexpr int kDeferPieces = 4;
 
-static int check_desc(const nmspmm_gemm_desc* d, int* mode_out)
+// any_rows: the caller's A is row-major and reaches the kernels through a padded transposed
+// copy, so M need not be a multiple of 4 (the col-major A's k rows must start on 16 bytes).
+static int check_desc(const nmspmm_gemm_desc* d, int* mode_out, bool any_rows = false)
 {
     if (!d) return NMSPMM_INVALID_ARGUMENT;
     if (d->M <= 0 || d->N <= 0 || d->K <= 0) return NMSPMM_INVALID_ARGUMENT;
-    if (d->M % 4 != 0 || d->N % kVecLenHost != 0 || d->K % 32 != 0) return NMSPMM_INVALID_ARGUMENT;
+    if ((!any_rows && d->M % 4 != 0) || d->N % kVecLenHost != 0 || d->K % 32 != 0) return NMSPMM_INVALID_ARGUMENT;
     if (d->layout_ns != 32 && d->layout_ns != 64 && d->layout_ns != 128) return NMSPMM_INVALID_ARGUMENT;
     if (d->N % d->layout_ns != 0) return NMSPMM_INVALID_ARGUMENT;
     if (d->split_k < 0) return NMSPMM_INVALID_ARGUMENT;
@@ -131,10 +133,10 @@ static int pick_tile(const nmspmm_gemm_desc* d, int sms)
     return (pad64 < pad128) ? kTile64x128 : kTile128x128;
 }
 
-static int make_plan(const nmspmm_gemm_desc* d, int sms, Plan* p)
+static int make_plan(const nmspmm_gemm_desc* d, int sms, Plan* p, bool any_rows = false)
 {
     int mode = 0;
-    int rc = check_desc(d, &mode);
+    int rc = check_desc(d, &mode, any_rows);
     if (rc != NMSPMM_OK) return rc;
     if (sms <= 0) sms = 148;
     if (d->path == NMSPMM_PATH_TF32) {
@@ -514,14 +516,15 @@ int nmspmm_gemm_plan(const nmspmm_gemm_desc* desc, nmspmm_gemm_plan_info* out)
 // The multiply with its outputs spelled out: n_out buffers, row stride ldc, first column col0.
 static int gemm_launch(const nmspmm_gemm_desc* desc, const float* A_dev, const float* B_dev, const int* D_dev,
                        const int* column_info_dev, float* const* C_out, int n_out, long long ldc, int col0,
-                       void* workspace_dev, size_t workspace_bytes, void* stream)
+                       void* workspace_dev, size_t workspace_bytes, void* stream, int lda = 0)
 {
     DeviceInfo* di = nullptr;
     int rc = device_info(&di);
     if (rc != NMSPMM_OK) return rc;
     Plan p;
-    rc = make_plan(desc, di->sms, &p);
+    rc = make_plan(desc, di->sms, &p, lda != 0);
     if (rc != NMSPMM_OK) return rc;
+    if (lda != 0 && (lda < desc->M || lda % 4 != 0)) return NMSPMM_INVALID_ARGUMENT;
     if (!A_dev || !B_dev || !D_dev || !C_out || n_out < 1 || n_out > kMaxOutputs) return NMSPMM_INVALID_ARGUMENT;
     if (desc->format == NMSPMM_FORMAT_HIGH && !column_info_dev) return NMSPMM_INVALID_ARGUMENT;
     if (!aligned16(A_dev) || !aligned16(B_dev) || !aligned16(D_dev)) return NMSPMM_INVALID_ARGUMENT;
@@ -539,6 +542,7 @@ static int gemm_launch(const nmspmm_gemm_desc* desc, const float* A_dev, const f
     outs.n_out = n_out;
     outs.ldc = ldc;
     outs.col0 = col0;
+    outs.lda = lda;
     a.status = di->status_word;
     a.M = desc->M;
     a.N = desc->N;
@@ -579,6 +583,38 @@ int nmspmm_gemm(const nmspmm_gemm_desc* desc, const float* A_dev, const float* B
     if (!desc) return NMSPMM_INVALID_ARGUMENT;
     float* out[1] = { C_dev };
     return gemm_launch(desc, A_dev, B_dev, D_dev, column_info_dev, out, 1, desc->N, 0, workspace_dev, workspace_bytes, stream);
+}
+
+// ---- A given row-major ----------------------------------------------------------------
+static size_t row_major_copy_bytes(const nmspmm_gemm_desc* d)
+{
+    const size_t ld = (static_cast<size_t>(d->M) + 3) / 4 * 4;
+    return round256(ld * static_cast<size_t>(d->K) * sizeof(float));
+}
+
+size_t nmspmm_gemm_row_major_workspace_bytes(const nmspmm_gemm_desc* desc)
+{
+    Plan p;
+    if (!desc || make_plan(desc, sm_count(), &p, true) != NMSPMM_OK) return 0;
+    return row_major_copy_bytes(desc) + p.counters_bytes + p.partial_bytes;
+}
+
+int nmspmm_gemm_row_major(const nmspmm_gemm_desc* desc, const float* A_rows_dev, const float* B_dev, const int* D_dev,
+                          const int* column_info_dev, float* C_dev, void* workspace_dev, size_t workspace_bytes, void* stream)
+{
+    if (!desc || !A_rows_dev || !workspace_dev || !aligned16(workspace_dev)) return NMSPMM_INVALID_ARGUMENT;
+    Plan p;
+    int rc = make_plan(desc, sm_count(), &p, true);
+    if (rc != NMSPMM_OK) return rc;
+    const size_t copy_bytes = row_major_copy_bytes(desc), own = p.counters_bytes + p.partial_bytes;
+    if (workspace_bytes < copy_bytes + own) return NMSPMM_WORKSPACE_TOO_SMALL;
+    const int ld = (desc->M + 3) / 4 * 4;
+    float* A_cols = static_cast<float*>(workspace_dev);
+    cudaError_t e = launch_transpose_rows(A_rows_dev, A_cols, desc->M, desc->K, ld, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(e);
+    float* out[1] = { C_dev };
+    return gemm_launch(desc, A_cols, B_dev, D_dev, column_info_dev, out, 1, desc->N, 0,
+                       own ? static_cast<unsigned char*>(workspace_dev) + copy_bytes : nullptr, own, stream, ld);
 }
 
 int nmspmm_gemm_gather(const nmspmm_gemm_desc* desc, const float* A_dev, const float* B_dev, const int* D_dev,

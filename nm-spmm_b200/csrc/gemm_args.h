@@ -63,6 +63,7 @@ struct GemmOutputs {
     int n_out;
     int col0;
     long long ldc;
+    int lda;               // host side only (tensor-map encoding): floats between consecutive k rows of A; 0 = M
 };
 NMSPMM_HD float* output_of(const GemmArgs& a, const GemmOutputs& o, int i) { return i == 0 ? a.C : o.C_more[i - 1]; }
 

@@ -402,7 +402,7 @@ cudaError_t launch_ffma(const GemmArgs& a, const GemmOutputs& outs, int grid, cu
         configured[dev] = true;
     }
     CUtensorMap map_a, map_b;
-    e = encode_tensor_map_2d(&map_a, a.A, a.M, a.sched.n_win * Cfg::KS, MS, Cfg::KS);
+    e = encode_tensor_map_2d(&map_a, a.A, outs.lda ? outs.lda : a.M, a.sched.n_win * Cfg::KS, MS, Cfg::KS);
     if (e != cudaSuccess) return e;
     // (test hook: a box one row short delivers fewer bytes than the stage's barrier expects,
     // so that the kernel's bounded waits run out; see nmspmm_test_short_fill)

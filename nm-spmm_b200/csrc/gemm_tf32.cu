@@ -443,9 +443,10 @@ static cudaError_t launch_tf32(const GemmArgs& a, const GemmOutputs& outs, int t
     }
     CUtensorMap map_a, map_b;
     const int K = a.sched.n_win * KW;
-    const int a_blocked = (a.M % 32 == 0) ? 1 : 0;
-    e = a_blocked ? encode_tensor_map_blocks32(&map_a, a.A, a.M, K, KW, 4)
-                  : encode_tensor_map_2d(&map_a, a.A, a.M, K, 32, KW, 1);
+    const int lda = outs.lda ? outs.lda : a.M;             // a row-major caller's transposed copy is padded to 4 columns
+    const int a_blocked = (lda % 32 == 0) ? 1 : 0;
+    e = a_blocked ? encode_tensor_map_blocks32(&map_a, a.A, lda, K, KW, 4)
+                  : encode_tensor_map_2d(&map_a, a.A, lda, K, 32, KW, 1);
     if (e != cudaSuccess) return e;
     e = encode_tensor_map_blocks32(&map_b, a.B, a.N, a.W, Cfg::WSP - (g_test_short_fill ? 1 : 0), QT);   // (test hook, see kernels.h)
     if (e != cudaSuccess) return e;

@@ -11,6 +11,9 @@ cudaError_t launch_retile(const int* DT, int* D, int W, int Q, int Qs, cudaStrea
 cudaError_t launch_preprocess_high(const int* DT, int* D, int* cinfo, int pm, int pn, int W, int Q, int Qs,
                                    int fuse, int tail_ints, cudaStream_t st);
 
+// in [M][K] row-major -> out [K][ld] (ld >= M, the extra columns zero).
+cudaError_t launch_transpose_rows(const float* in, float* out, int M, int K, int ld, cudaStream_t st);
+
 // One compiled FFMA kernel variant.
 struct FfmaVariant {
     int tile_id;        // nmspmm_tile

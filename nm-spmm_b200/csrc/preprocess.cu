@@ -138,4 +138,30 @@ cudaError_t launch_preprocess_high(const int* DT, int* D, int* cinfo, int pm, in
     return e;
 }
 
+// Row-major activations [M][K] -> the reference's col-major A, i.e. [K][ld] with ld >= M,
+// columns M .. ld-1 zero.  32 x 32 patches through padded shared memory: reads coalesced
+// along k, writes coalesced along m.  HBM-bound: 4 M K bytes in, 4 ld K out.
+__global__ void __launch_bounds__(256) transpose_rows_kernel(const float* __restrict__ in, float* __restrict__ out, int M, int K, int ld)
+{
+    __shared__ float patch[32][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int k0 = blockIdx.x * 32, m0 = blockIdx.y * 32;
+    for (int j = ty; j < 32; j += 8) {
+        const int m = m0 + j, k = k0 + tx;
+        patch[j][tx] = (m < M && k < K) ? in[static_cast<size_t>(m) * K + k] : 0.0f;
+    }
+    __syncthreads();
+    for (int j = ty; j < 32; j += 8) {
+        const int k = k0 + j, m = m0 + tx;
+        if (k < K && m < ld) out[static_cast<size_t>(k) * ld + m] = patch[tx][j];
+    }
+}
+
+cudaError_t launch_transpose_rows(const float* in, float* out, int M, int K, int ld, cudaStream_t st)
+{
+    const dim3 grid((K + 31) / 32, (ld + 31) / 32);
+    transpose_rows_kernel<<<grid, 256, 0, st>>>(in, out, M, K, ld);
+    return cudaGetLastError();
+}
+
 }  // namespace nmspmm

@@ -1,5 +1,6 @@
 """The sparse linear layer: prune + compress + pack on the device, then the multiply,
-against a dense FP32 product with the layer's own pruned weight."""
+against a dense FP32 product with the layer's own pruned weight; the row-major-A entry
+point on its own; the torch.library registration (fake kernel, autograd)."""
 import numpy as np
 import pytest
 import torch
@@ -35,3 +36,50 @@ def test_sparse_linear_tf32_path(pkg):
     x = torch.randn(200, 512, device="cuda")
     want = x.double() @ layer.dense_weight().double().t()
     assert float((layer(x).double() - want).norm() / want.norm()) <= 2e-3
+
+
+@pytest.mark.parametrize("M", [1, 3, 16, 130, 257])
+@pytest.mark.parametrize("n_keep,path", [(16, 0), (8, 0), (4, 0), (8, 1), (12, 1)])
+def test_row_major_activations_against_the_checker(pkg, orc, M, n_keep, path):
+    """nmspmm_gemm_row_major: A[i*K + k], any M >= 1 (the col-major copy the kernels read is
+    padded to 4 rows by the transposing kernel), checked against the CPU checker."""
+    p = pkg.formats.make_random(M + (-M) % 4, 384, 512, n_keep, seed=400 + M)
+    A_rows = np.ascontiguousarray(p.A_km.T[:M])                          # (M, K) row-major
+    op = pkg.NMSpMM.from_problem(p)
+    got = op.matmul_rows(torch.from_numpy(A_rows).cuda(), path=path)
+    torch.cuda.synchronize()
+    assert pkg.device_status() == 0 and got.shape == (M, 384)
+    sub = np.ascontiguousarray(p.A_km[:, :M])
+    if path == 0:
+        want, tol = orc.nm_gemm_f32(sub, p.B_col, p.D_col), 1e-5
+    else:
+        want, tol = orc.nm_gemm_f64(sub, p.B_col, p.D_col), 2e-3
+    err = float(np.linalg.norm(got.cpu().numpy().astype(np.float64) - want) / np.linalg.norm(want))
+    assert err <= tol, err
+
+
+def test_custom_op_is_registered_with_fake_kernel_and_autograd(pkg):
+    torch.manual_seed(7)
+    w = torch.randn(256, 128, device="cuda") * 0.1
+    layer = pkg.linear.NMSparseLinear(pkg, w, 16)
+    op = torch.ops.nmspmm_b200.sparse_linear
+    x = torch.randn(8, 128, device="cuda", requires_grad=True)
+    layer.values.requires_grad_(True)
+    args = (x, layer.values, layer.op.D, layer.op.column_info, layer.raw_indices, 16, layer.op.format, layer.op.layout_ns, 32, 0)
+    torch.library.opcheck(op, args, test_utils=("test_schema", "test_faketensor", "test_autograd_registration"))
+    # gradients against a dense product with the pruned weight
+    y = layer(x)
+    y.square().sum().backward()
+    gx, gv = x.grad.clone(), layer.values.grad.clone()
+    wd = layer.dense_weight().detach().requires_grad_(True)
+    x2 = x.detach().clone().requires_grad_(True)
+    (x2 @ wd.t()).square().sum().backward()
+    assert float((gx - x2.grad).norm() / x2.grad.norm()) <= 1e-4
+    rows = pkg.linear._dense_rows(layer.raw_indices, 16)
+    assert float((gv - wd.grad.t().gather(0, rows)).norm() / gv.norm()) <= 1e-4
+    # shape inference without running the kernel
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    mode = FakeTensorMode()
+    fake = [mode.from_tensor(a.detach()) if isinstance(a, torch.Tensor) else a for a in args]
+    with mode:
+        assert op(*fake).shape == (8, 256)
