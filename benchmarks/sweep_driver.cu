@@ -1,16 +1,23 @@
-// Timing sweep over the reference's headline benchmark shapes, written against the public
+// Timing sweeps of the reference's two benchmark suites, written against the public
 // interface include/NM-SpMM.h only, so that the same source links either to the reference's
 // own kernels (recompiled for sm_100a) or to this repository's library.  Measurement
 // infrastructure: not part of the product, not a parity check (no result is compared).
 //
-// Shapes: the 5 x 20 grid of benchmark/kernel_performance/run_test/nmspmm/run_nmspmm.sh:16-18
-// of the reference (M in {256 .. 4096}, twenty (N, K) pairs of LLM linear layers), for one
-// sparsity.  As in that script, a shape's figure is the best dense-equivalent TFLOP/s
-// (2 M N K / t, tests/test_nmspmm.cu:139) over the four entry points that accept the shape
-// and SPLIT_K in {1, 2, 4, 8}.  Inputs are seeded pseudo-random operands in the reference's
-// formats (values do not matter for the timing; indices are valid sorted N:M indices).
+// Default mode -- the 5 x 20 grid of benchmark/kernel_performance/run_test/nmspmm/
+// run_nmspmm.sh:16-18 of the reference (M in {256 .. 4096}, twenty (N, K) pairs of LLM linear
+// layers), for one sparsity.  As in that script, a shape's figure is the best
+// dense-equivalent TFLOP/s (2 M N K / t, tests/test_nmspmm.cu:139) over the four entry points
+// that accept the shape and SPLIT_K in {1, 2, 4, 8}.
+//
+// Table mode (first argument "table") -- benchmark/different_kernel/run_nmspmm.sh:16-37: six
+// square-ish shapes, one line per (shape, entry point) with the dense-equivalent TFLOP/s of
+// each SPLIT_K in {1, 2, 4, 8}.
+//
+// Inputs are seeded pseudo-random operands in the reference's formats (values do not matter
+// for the timing; indices are valid sorted N:M indices).
 //
 // usage: sweep <sparsity> [iterations] [m ...]       (one line per shape on stdout)
+//        sweep table <sparsity> [iterations]         (one line per shape and entry point)
 #include <cuda_runtime.h>
 
 #include <algorithm>
@@ -18,6 +25,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
+#include <string>
 #include <vector>
 
 #include "NM-SpMM.h"
@@ -45,8 +53,10 @@ struct Entry { const char* name; int ms, ns, layout; LowFn low; HighFn high; };
 
 int main(int argc, char** argv)
 {
+    const bool table = argc > 1 && std::string(argv[1]) == "table";
+    if (table) { --argc; ++argv; }
     if (argc < 2) {
-        fprintf(stderr, "usage: %s <sparsity> [iterations] [m ...]\n", argv[0]);
+        fprintf(stderr, "usage: %s [table] <sparsity> [iterations] [m ...]\n", argv[0]);
         return 2;
     }
     const float sparsity = static_cast<float>(atof(argv[1]));
@@ -54,6 +64,9 @@ int main(int argc, char** argv)
     std::vector<int> Ms;
     for (int i = 3; i < argc; ++i) Ms.push_back(atoi(argv[i]));
     if (Ms.empty()) Ms = { 256, 512, 1024, 2048, 4096 };
+    const int tM[6] = { 512, 512, 512, 1024, 2048, 4096 }, tN[6] = { 512, 1024, 2048, 2048, 4096, 4096 },
+              tK[6] = { 512, 1024, 2048, 2048, 4096, 4096 };
+    if (table) Ms.assign(1, 0);
     const int Ns[20] = { 2048, 6144, 2048, 5632, 4096, 12288, 4096, 11008, 5120, 15360, 5120, 13824, 6656, 19968, 6656, 17920, 8192, 24576, 8192, 22016 };
     const int Ks[20] = { 2048, 2048, 5632, 2048, 4096, 4096, 11008, 4096, 5120, 5120, 13824, 5120, 6656, 6656, 17920, 6656, 8192, 8192, 22016, 8192 };
     const Entry entries[4] = {
@@ -63,14 +76,14 @@ int main(int argc, char** argv)
         { "huge", 64, 128, 128, nmGEMM_huge_matrices_low_sparsity, nmGEMM_huge_matrices_high_sparsity },
     };
     const int n_keep = static_cast<int>(std::lround(32 * (1.0 - sparsity)));
-    const bool high = sparsity > 0.7f;
+    const bool high = sparsity > 0.7f;                    // 75 % and 87.5 % go through the high-sparsity entry points
     cudaEvent_t e0, e1;
     CK(cudaEventCreate(&e0));
     CK(cudaEventCreate(&e1));
     printf("# sparsity %.3f, n_keep %d, %d timed launches per configuration\n", sparsity, n_keep, iters);
-    for (int M : Ms) {
-        for (int s = 0; s < 20; ++s) {
-            const int N = Ns[s], K = Ks[s];
+    for (int M0 : Ms) {
+        for (int s = 0; s < (table ? 6 : 20); ++s) {
+            const int M = table ? tM[s] : M0, N = table ? tN[s] : Ns[s], K = table ? tK[s] : Ks[s];
             const int W = K / 32 * n_keep, Q = N / VEC_LEN;
             // operands in the reference's formats
             std::vector<float> hA(static_cast<size_t>(M) * K), hB(static_cast<size_t>(W) * N);
@@ -119,6 +132,7 @@ int main(int argc, char** argv)
                 }
                 for (const Entry& en : entries) {
                     if (en.layout != layout || M % en.ms != 0 || N % en.ns != 0) continue;
+                    if (table) printf("%d %d %d %s", M, N, K, en.name);
                     for (int split : { 1, 2, 4, 8 }) {
                         auto launch = [&]() {       // like the reference's own timing loop: C is not cleared between launches
                             if (high) en.high(dA, dB, dD, dCI, dC, M, N, K, W, sparsity, split);
@@ -134,13 +148,16 @@ int main(int argc, char** argv)
                         CK(cudaEventElapsedTime(&ms, e0, e1));
                         const double tf = 2.0 * M * N * K / (ms / iters * 1e-3) / 1e12;
                         if (tf > best) { best = tf; best_entry = en.name; best_split = split; }
+                        if (table) printf(" %.3f", tf);
                     }
+                    if (table) printf("\n");
                 }
                 CK(cudaFree(dD));
                 if (dCI) CK(cudaFree(dCI));
             }
             CK(cudaGetLastError());
-            printf("%d %d %d %.3f %s %d\n", M, N, K, best, best_entry, best_split);
+            if (table) printf("%d %d %d best %.3f %s %d\n", M, N, K, best, best_entry, best_split);
+            else printf("%d %d %d %.3f %s %d\n", M, N, K, best, best_entry, best_split);
             fflush(stdout);
             CK(cudaFree(dA));
             CK(cudaFree(dB));

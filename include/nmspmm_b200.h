@@ -121,11 +121,15 @@ typedef struct nmspmm_gemm_desc {
 } nmspmm_gemm_desc;
 
 /* Bytes of scratch the multiply needs for this description (0 when every unit range is a
- * whole tile).  The scratch holds per-tile arrival counters followed by slots for tile
- * pieces.  The caller need not initialise it and may hand the same buffer to multiplies of
- * different descriptions one after the other on a stream: a multiply that uses the counters
- * clears them itself (a cudaMemsetAsync on `stream` ahead of the kernel).  Two multiplies
- * that overlap on the GPU need two buffers. */
+ * whole tile).  The scratch starts with a block of per-tile arrival counters,
+ * NMSPMM_COUNTER_BYTES for every description of up to 16384 tiles, followed by slots for tile
+ * pieces.  The counter block must be zero before the first use (cudaMemset once, e.g. of the
+ * whole buffer); every multiply leaves it zero, and no multiply writes anything else there,
+ * so one buffer can serve descriptions of different shapes, paths and splits one after the
+ * other on a stream.  Two multiplies that overlap on the GPU need two buffers.  After
+ * NMSPMM_DEVICE_TIMEOUT has been reported the library clears the block itself ahead of every
+ * multiply (a CTA that gave up did not arrive at its counter). */
+#define NMSPMM_COUNTER_BYTES (64u << 10)
 size_t nmspmm_gemm_workspace_bytes(const nmspmm_gemm_desc* desc);
 
 /* Replaces the eight nmGEMM_*_matrices_{low,high}_sparsity launchers
@@ -245,6 +249,21 @@ int nmspmm_release_cached(void);
  * scalar FFMA, packed = 1 the two-lane packed FMA of sm_100.  The FP32 roofline
  * denominator is the larger of the two. */
 int nmspmm_measure_ffma_peak(double* tflops_out, int packed, void* stream);
+
+/* ------------------------------------------------------------------ tuned plans
+ * The reference picks, per shape, the best of its four tilings x SPLIT_K in {1,2,4,8} by an
+ * exhaustive sweep outside the library (benchmark/kernel_performance/run_test/nmspmm/
+ * run_nmspmm.sh:16-38).  Here the result of such a sweep (nm-spmm_b200/tuner.py) lives in a
+ * table the planner consults: a description with tile = 0 and split_k = 0 that matches an entry
+ * on (M, N, K, n_keep, format, path, vec_len) gets the entry's tile and split_k (0 = the
+ * library's automatic schedule on that tile) instead of the built-in heuristics.  The table
+ * is read once per process from the text file named by the environment variable
+ * NMSPMM_TUNED_PLANS (set but empty: none), else from tuned_plans.txt beside the library;
+ * one entry per line, "M N K n_keep format path vec_len tile split_k", '#' starts a comment. */
+int nmspmm_tuned_plan_set(const nmspmm_gemm_desc* key, int tile, int split_k);   /* add or replace one entry */
+int nmspmm_tuned_plan_load(const char* path);                                    /* merge a file into the table */
+int nmspmm_tuned_plan_clear(void);
+int nmspmm_tuned_plan_count(void);
 
 /* ------------------------------------------------------------------ testing
  * Makes the bounded device-side waits run out without faulting or hanging anything: while

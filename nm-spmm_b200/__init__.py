@@ -18,7 +18,7 @@ from typing import Optional
 
 import numpy as np
 
-from . import build, formats, linear, sharding  # noqa: F401  (in-tree nvcc build; seeded operands; layer; multi-GPU partition)
+from . import build, formats, linear, sharding, tuner  # noqa: F401  (in-tree nvcc build; seeded operands; layer; multi-GPU partition; plan tuner)
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 # NMSPMM_LIBRARY selects another build of the same library (A/B comparisons of kernels).
@@ -34,7 +34,8 @@ C_ABI_SYMBOLS = (
     "nmspmm_status_string", "nmspmm_last_cuda_error", "nmspmm_version",
     "nmspmm_trans_index_device", "nmspmm_preprocess_low_device", "nmspmm_preprocess_high_device",
     "nmspmm_trans_index_host", "nmspmm_preprocess_low_host", "nmspmm_preprocess_high_host",
-    "nmspmm_test_short_fill", "nmspmm_gemm_workspace_bytes", "nmspmm_gemm", "nmspmm_gemm_row_major",
+    "nmspmm_test_short_fill", "nmspmm_tuned_plan_set", "nmspmm_tuned_plan_load", "nmspmm_tuned_plan_clear",
+    "nmspmm_tuned_plan_count", "nmspmm_gemm_workspace_bytes", "nmspmm_gemm", "nmspmm_gemm_row_major",
     "nmspmm_gemm_row_major_workspace_bytes", "nmspmm_gemm_with_cached_workspace", "nmspmm_device_status",
     "nmspmm_gemm_plan", "nmspmm_gemm_host", "nmspmm_release_cached", "nmspmm_measure_ffma_peak",
     "nmspmm_gemm_static_scratch", "nmspmm_gemm_gather", "nmspmm_prune_device",
@@ -88,6 +89,8 @@ def load_library():
     lib.nmspmm_gemm_workspace_bytes.restype = sz
     lib.nmspmm_gemm_workspace_bytes.argtypes = [ctypes.POINTER(GemmDesc)]
     lib.nmspmm_gemm.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp, vp, sz, vp]
+    lib.nmspmm_tuned_plan_set.argtypes = [ctypes.POINTER(GemmDesc), ci, ci]
+    lib.nmspmm_tuned_plan_load.argtypes = [ctypes.c_char_p]
     lib.nmspmm_gemm_row_major_workspace_bytes.restype = sz
     lib.nmspmm_gemm_row_major_workspace_bytes.argtypes = [ctypes.POINTER(GemmDesc)]
     lib.nmspmm_gemm_row_major.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp, vp, sz, vp]
@@ -293,6 +296,46 @@ def device_status(clear: bool = True) -> int:
     if rc not in (OK, DEVICE_TIMEOUT):
         raise NMSpMMError("nmspmm_device_status", rc)
     return word.value
+
+
+_tuned_shadow = {}      # what this process has registered through the functions below (the C table has no read-back)
+
+
+def set_tuned_plan(desc: GemmDesc, tile: int, split_k: int) -> None:
+    """nmspmm_tuned_plan_set: descriptions like ``desc`` that leave tile and split to the library get these."""
+    _check("nmspmm_tuned_plan_set", load_library().nmspmm_tuned_plan_set(ctypes.byref(desc), tile, split_k))
+    _tuned_shadow[(desc.M, desc.N, desc.K, desc.n_keep, desc.format, desc.path, 64 if desc.vec_len == 64 else 32)] = (tile, split_k)
+
+
+def load_tuned_plans(path: str) -> int:
+    """Merges a table file (see tuner.py) into the running library.  Returns the entry count."""
+    _check("nmspmm_tuned_plan_load", load_library().nmspmm_tuned_plan_load(path.encode()))
+    _tuned_shadow.update(tuner.read_table(path))
+    return int(load_library().nmspmm_tuned_plan_count())
+
+
+def clear_tuned_plans() -> None:
+    _check("nmspmm_tuned_plan_clear", load_library().nmspmm_tuned_plan_clear())
+    _tuned_shadow.clear()
+
+
+def tuned_plans_snapshot_and_clear():
+    """For the tuner: candidates must be timed against the bare heuristics."""
+    saved = dict(_tuned_shadow)
+    default = tuner.default_table_path()
+    env = os.environ.get("NMSPMM_TUNED_PLANS")
+    src = env if env is not None else default
+    if src and os.path.exists(src):
+        saved = {**tuner.read_table(src), **saved}
+    clear_tuned_plans()
+    return saved
+
+
+def tuned_plans_restore(saved) -> None:
+    clear_tuned_plans()
+    for key, (tile, split) in saved.items():
+        M, N, K, n_keep, fmt, path, vec = key
+        set_tuned_plan(make_desc(M, N, K, n_keep, fmt, 32, path, 0, 0, vec), tile, split)
 
 
 def test_short_fill(enable: bool) -> int:

@@ -1,9 +1,13 @@
 // C-ABI of the library (include/nmspmm_b200.h): argument checks, plan selection
 // (tile + split-K), scratch layout, and the host-buffer convenience forms.
 #include <cuda_runtime.h>
+#include <dlfcn.h>
 #include <mutex>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
+#include <string>
+#include <vector>
 
 #include "kernels.h"
 #include "nmspmm_b200.h"
@@ -93,6 +97,21 @@ struct Plan {
     size_t counters_bytes = 0, partial_bytes = 0;
 };
 
+// The scratch of a split multiply starts with the per-tile arrival counters.  Their block has
+// one size, NMSPMM_COUNTER_BYTES, for every plan of up to 16384 tiles (larger plans round up
+// to a multiple of it), and every plan's slots start behind it, whether the plan uses the
+// counters or not: whatever the shapes, paths and splits a buffer serves in turn, the block is
+// only ever written by the arrival logic, which leaves it zero.
+constexpr size_t kCounterBlock = NMSPMM_COUNTER_BYTES;
+static size_t counter_block_bytes(long long n_tiles)
+{
+    const size_t need = static_cast<size_t>(n_tiles) * sizeof(unsigned);
+    return need <= kCounterBlock ? kCounterBlock : (need + kCounterBlock - 1) / kCounterBlock * kCounterBlock;
+}
+// Set once a bounded wait has been seen to give up in this process: a CTA that left early
+// did not arrive at its counter, so from then on every multiply clears the block itself.
+static bool g_timeout_seen = false;
+
 // Pieces per tile from which the reduction moves out of the multiply into its own
 // kernel.  One CTA adding p pieces walks them one after the other (about 1.5 us per piece
 // of a 128 x 128 tile); the kernel spreads that over the GPU for one launch (2-3 us).
@@ -133,11 +152,89 @@ static int pick_tile(const nmspmm_gemm_desc* d, int sms)
     return (pad64 < pad128) ? kTile64x128 : kTile128x128;
 }
 
-static int make_plan(const nmspmm_gemm_desc* d, int sms, Plan* p, bool any_rows = false)
+// ---- tuned plans ------------------------------------------------------------------
+// (M, N, K, n_keep, format, path, vec_len) -> tile and split_k found by measurement
+// (nm-spmm_b200/tuner.py).  A description that leaves both choices to the library
+// (tile = 0, split_k = 0) takes a matching entry instead of the heuristics below.  The
+// table is read once per process from the text file named by NMSPMM_TUNED_PLANS, else
+// from tuned_plans.txt beside the library; nmspmm_tuned_plan_set adds entries at run time.
+struct TunedPlan { int M, N, K, n_keep, format, path, vec_len, tile, split_k; };
+static std::vector<TunedPlan> g_tuned;
+static std::mutex g_tuned_mutex;
+static bool g_tuned_loaded = false;
+
+static int vec_of(int v) { return v == 64 ? 64 : 32; }
+
+static void tuned_set_locked(const TunedPlan& t)
+{
+    for (TunedPlan& e : g_tuned)
+        if (e.M == t.M && e.N == t.N && e.K == t.K && e.n_keep == t.n_keep && e.format == t.format && e.path == t.path &&
+            e.vec_len == t.vec_len) {
+            e = t;
+            return;
+        }
+    g_tuned.push_back(t);
+}
+
+static int tuned_load_file_locked(const char* path)
+{
+    FILE* f = fopen(path, "r");
+    if (!f) return -1;
+    char line[256];
+    int n = 0;
+    while (fgets(line, sizeof line, f)) {
+        TunedPlan t;
+        if (line[0] == '#') continue;
+        if (sscanf(line, "%d %d %d %d %d %d %d %d %d", &t.M, &t.N, &t.K, &t.n_keep, &t.format, &t.path, &t.vec_len, &t.tile,
+                   &t.split_k) == 9 && t.tile >= 0 && t.tile < kTileCount && t.split_k >= 0) {
+            t.vec_len = vec_of(t.vec_len);
+            tuned_set_locked(t);
+            ++n;
+        }
+    }
+    fclose(f);
+    return n;
+}
+
+static void tuned_load_default_locked()
+{
+    if (g_tuned_loaded) return;
+    g_tuned_loaded = true;
+    if (const char* env = getenv("NMSPMM_TUNED_PLANS")) {
+        if (env[0]) tuned_load_file_locked(env);
+        return;                                            // set but empty: no table
+    }
+    Dl_info info;
+    if (dladdr(reinterpret_cast<const void*>(&tuned_load_default_locked), &info) && info.dli_fname) {
+        std::string dir(info.dli_fname);
+        const size_t slash = dir.rfind('/');
+        dir = (slash == std::string::npos) ? std::string(".") : dir.substr(0, slash);
+        tuned_load_file_locked((dir + "/tuned_plans.txt").c_str());
+    }
+}
+
+static bool tuned_lookup(const nmspmm_gemm_desc* d, int* tile, int* split_k)
+{
+    std::lock_guard<std::mutex> lock(g_tuned_mutex);
+    tuned_load_default_locked();
+    for (const TunedPlan& e : g_tuned)
+        if (e.M == d->M && e.N == d->N && e.K == d->K && e.n_keep == d->n_keep && e.format == d->format && e.path == d->path &&
+            e.vec_len == vec_of(d->vec_len)) {
+            *tile = e.tile;
+            *split_k = e.split_k;
+            return true;
+        }
+    return false;
+}
+
+static int make_plan(const nmspmm_gemm_desc* d_in, int sms, Plan* p, bool any_rows = false)
 {
     int mode = 0;
-    int rc = check_desc(d, &mode, any_rows);
+    int rc = check_desc(d_in, &mode, any_rows);
     if (rc != NMSPMM_OK) return rc;
+    nmspmm_gemm_desc tuned = *d_in;
+    const nmspmm_gemm_desc* d = d_in;
+    if (d_in->tile == 0 && d_in->split_k == 0 && tuned_lookup(d_in, &tuned.tile, &tuned.split_k)) d = &tuned;
     if (sms <= 0) sms = 148;
     if (d->path == NMSPMM_PATH_TF32) {
         // Tensor-core path: one CTA per tile and K slice.  Tile 128 x 256 with one CTA per
@@ -200,6 +297,7 @@ static int make_plan(const nmspmm_gemm_desc* d, int sms, Plan* p, bool any_rows 
             p->deferred = true;
             p->first_split_tile = p->n_dp;
             p->n_split_tiles = static_cast<int>(sliced_tiles);
+            p->counters_bytes = counter_block_bytes(nt);      // unused by this path; keeps the slots off the counter block
             p->partial_bytes = static_cast<size_t>(p->slots) * 128 * want_ns * sizeof(float);
         }
         return NMSPMM_OK;
@@ -271,7 +369,7 @@ static int make_plan(const nmspmm_gemm_desc* d, int sms, Plan* p, bool any_rows 
     }
     p->grid = p->n_virtual;      // one unit range per CTA (the automatic schedule never exceeds the resident count)
     if (p->slots > 0) {
-        p->counters_bytes = (static_cast<size_t>(p->n_tiles) * sizeof(unsigned) + 255) / 256 * 256;
+        p->counters_bytes = counter_block_bytes(p->n_tiles);
         p->partial_bytes = static_cast<size_t>(p->slots) * v->ms * v->ns * sizeof(float);
     }
     return NMSPMM_OK;
@@ -559,10 +657,9 @@ static int gemm_launch(const nmspmm_gemm_desc* desc, const float* A_dev, const f
         if (workspace_bytes < p.counters_bytes + p.partial_bytes) return NMSPMM_WORKSPACE_TOO_SMALL;
         a.counters = p.deferred ? nullptr : static_cast<unsigned*>(workspace_dev);
         a.partial = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace_dev) + p.counters_bytes);
-        if (a.counters) {
-            // Where the counters end and the slots begin depends on the plan (tile count, path,
-            // split), so a buffer that served another plan may hold slot data here.  Clear the
-            // counters on the stream ahead of every launch that reads them.
+        if (a.counters && (p.counters_bytes > kCounterBlock || g_timeout_seen)) {
+            // a block larger than the common one overlaps other plans' slots; and after a
+            // timeout somewhere the counters can no longer be trusted to have been left zero
             cudaError_t me = cudaMemsetAsync(workspace_dev, 0, p.counters_bytes, static_cast<cudaStream_t>(stream));
             if (me != cudaSuccess) return cuda_fail(me);
         }
@@ -632,6 +729,7 @@ int nmspmm_device_status(int* status_out, int clear)
     int word = 0;
     cudaError_t e = cudaMemcpy(&word, di->status_word, sizeof(int), cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return cuda_fail(e);
+    if (word != 0) g_timeout_seen = true;
     if (word != 0 && clear) {
         e = cudaMemset(di->status_word, 0, sizeof(int));
         if (e != cudaSuccess) return cuda_fail(e);
@@ -786,6 +884,7 @@ int nmspmm_gemm_host(const nmspmm_gemm_desc* desc, const float* A_host, const fl
     else
         rc = nmspmm_preprocess_low_device(dDT, dD, W, Q, desc->layout_ns, st);
     if (rc != NMSPMM_OK) return rc;
+    if (ws_b > 0) NMSPMM_TRY(cudaMemsetAsync(dWS, 0, kCounterBlock, st));   // the arena is carved anew per call: its counter block starts zero
     for (int c = 0; c < n_chunks; ++c) {
         const int r0 = c * chunk_rows, rows = (c + 1 < n_chunks) ? chunk_rows : M - r0;
         nmspmm_gemm_desc dc = *desc;
@@ -804,6 +903,39 @@ int nmspmm_gemm_host(const nmspmm_gemm_desc* desc, const float* A_host, const fl
     NMSPMM_TRY(cudaStreamSynchronize(st));
 #undef NMSPMM_TRY
     return nmspmm_device_status(nullptr, 1);
+}
+
+int nmspmm_tuned_plan_set(const nmspmm_gemm_desc* key, int tile, int split_k)
+{
+    int mode = 0;
+    if (check_desc(key, &mode, true) != NMSPMM_OK || tile < 0 || tile >= kTileCount || split_k < 0) return NMSPMM_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(g_tuned_mutex);
+    tuned_load_default_locked();
+    tuned_set_locked(TunedPlan { key->M, key->N, key->K, key->n_keep, key->format, key->path, vec_of(key->vec_len), tile, split_k });
+    return NMSPMM_OK;
+}
+
+int nmspmm_tuned_plan_load(const char* path)
+{
+    if (!path) return NMSPMM_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(g_tuned_mutex);
+    g_tuned_loaded = true;                                 // an explicit load replaces the default look-up
+    return tuned_load_file_locked(path) >= 0 ? NMSPMM_OK : NMSPMM_INVALID_ARGUMENT;
+}
+
+int nmspmm_tuned_plan_clear(void)
+{
+    std::lock_guard<std::mutex> lock(g_tuned_mutex);
+    g_tuned_loaded = true;
+    g_tuned.clear();
+    return NMSPMM_OK;
+}
+
+int nmspmm_tuned_plan_count(void)
+{
+    std::lock_guard<std::mutex> lock(g_tuned_mutex);
+    tuned_load_default_locked();
+    return static_cast<int>(g_tuned.size());
 }
 
 int nmspmm_test_short_fill(int enable)

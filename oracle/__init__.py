@@ -33,10 +33,23 @@ _f32p = ctypes.POINTER(ctypes.c_float)
 _f64p = ctypes.POINTER(ctypes.c_double)
 
 
+def reference_checkout() -> str:
+    """Where the reference's sources lie, if anywhere: the directory named by
+    NMSPMM_REFERENCE_DIR, else a checkout called ``reference`` beside this repository."""
+    for cand in (os.environ.get("NMSPMM_REFERENCE_DIR"), os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")):
+        if cand and os.path.exists(os.path.join(cand, "src", "preprocessing.cu")):
+            return cand
+    return ""
+
+
 def build(verbose: bool = False) -> None:
     """Compile the C restatement (and the reference objects when the reference
     checkout is present).  Building the checker is not using it."""
-    out = subprocess.run(["make", "-C", _HERE, "all"], capture_output=True, text=True)
+    cmd = ["make", "-C", _HERE, "all"]
+    ref = reference_checkout()
+    if ref:
+        cmd.append("REF=" + ref)
+    out = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or out.returncode != 0:
         print(out.stdout + out.stderr)
     if out.returncode != 0:

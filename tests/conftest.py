@@ -3,6 +3,10 @@ import sys
 
 import pytest
 
+# The tests exercise the planner's own heuristics: no tuned-plan table (tests that want
+# entries register them through the API).
+os.environ["NMSPMM_TUNED_PLANS"] = ""
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)

@@ -117,7 +117,7 @@ def test_split_k_fills_the_machine_for_skinny_shapes(pkg):
     tdeep = pkg.make_desc(128, 1024, 131072, 4, 1, 128, path=pkg.PATH_TF32)
     info = pkg.plan(tdeep)
     assert info.tile_n == 128 and info.split_k == 296 // 8 and info.grid == 8 * info.split_k
-    assert pkg.workspace_bytes(tdeep) == info.grid * 128 * 128 * 4
+    assert pkg.workspace_bytes(tdeep) == (64 << 10) + info.grid * 128 * 128 * 4      # counter block + one slot per slice
     # 512 tiles on 148 one-CTA SMs: three whole waves, the 68 tiles of the last one in two slices each
     tbig = pkg.plan(pkg.make_desc(4096, 4096, 4096, 8, 1, 128, path=pkg.PATH_TF32))
     assert tbig.tile_n == 256 and tbig.n_dp == 444 and tbig.split_k == 2 and tbig.grid == 444 + 2 * 68
@@ -163,3 +163,31 @@ def test_partition_columns(pkg_host):
         sh.partition_columns(256, 4, 128)
     with pytest.raises(ValueError):
         sh.partition_columns(200, 1, 128)
+
+
+def test_tuned_plan_table_overrides_the_heuristics_and_only_them(pkg, tmp_path):
+    d = pkg.make_desc(256, 2048, 2048, 4, 1, 128)
+    base = pkg.plan(d)
+    try:
+        pkg.set_tuned_plan(d, 2, 4)                                    # tile 64 x 128, four K slices
+        tuned = pkg.plan(d)
+        assert (tuned.tile_m, tuned.tile_n, tuned.split_k) == (64, 128, 4)
+        # a caller that names a tile or a split keeps its own choice
+        own = pkg.plan(pkg.make_desc(256, 2048, 2048, 4, 1, 128, tile=1))
+        assert (own.tile_m, own.tile_n) == (128, 128)
+        assert pkg.plan(pkg.make_desc(256, 2048, 2048, 4, 1, 128, split_k=2)).split_k == 2
+        # other shapes are untouched
+        other = pkg.plan(pkg.make_desc(512, 2048, 2048, 4, 1, 128))
+        assert (other.tile_m, other.tile_n) == (pkg.plan(pkg.make_desc(512, 2048, 2048, 4, 1, 128, tile=0)).tile_m, other.tile_n)
+        # the file form
+        table = tmp_path / "plans.txt"
+        pkg.tuner.write_table(str(table), [((128, 1024, 4096, 8, 1, 0, 32), 3, 2, 1.0, 2.0), ((64, 256, 256, 16, 0, 0, 32), 0, 0, 1.0, 1.0)])
+        assert pkg.tuner.read_table(str(table)) == {(128, 1024, 4096, 8, 1, 0, 32): (3, 2)}
+        pkg.clear_tuned_plans()
+        assert pkg.load_tuned_plans(str(table)) == 1
+        got = pkg.plan(pkg.make_desc(128, 1024, 4096, 8, 1, 128))
+        assert (got.tile_m, got.split_k) == (32, 2)
+    finally:
+        pkg.clear_tuned_plans()
+    again = pkg.plan(d)
+    assert (again.tile_m, again.tile_n, again.split_k) == (base.tile_m, base.tile_n, base.split_k)
