@@ -174,6 +174,19 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void* tenso
         : "memory");
 }
 
+// Programmatic dependent launch.  grid_dependency_wait: returns once the kernel ahead of this
+// one on the stream has completed and its writes are visible (at once when this launch has
+// no such dependency).  grid_launch_dependents: this CTA no longer stands in the way of the
+// next kernel's CTAs being scheduled (they still wait, as above, for this grid to complete).
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Starts fetching a tensor map (kernel parameter) into the TMA unit's descriptor cache.
+__device__ __forceinline__ void prefetch_tensor_map(const void* tensor_map)
+{
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tensor_map)) : "memory");
+}
+
 // Tiled 3-D tensor copy global -> shared ({x, y, z} = element coordinates of the box corner).
 __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tensor_map, int x, int y, int z, uint32_t bar)
 {

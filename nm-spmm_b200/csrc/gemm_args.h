@@ -21,6 +21,8 @@ enum nmspmm_tile {
     kTile32x128 = 3,
     kTile16x128 = 4,
     kTile128x256 = 5,
+    kTile16x256 = 6,      // skinny activations: 1 KB of every B row per CTA, eight warps
+    kTile32x256 = 7,
     kTileCount
 };
 

@@ -94,6 +94,8 @@ __device__ __forceinline__ void nm_gemm_ffma_body(const GemmArgs& g, const CUten
     const int warp = tid >> 5, lane = tid & 31;
 
     if (tid == 0) {
+        prefetch_tensor_map(&map_a);                       // the first copies would otherwise wait for the descriptors
+        prefetch_tensor_map(&map_b);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bars + s * 8, 1);                    // full: one arrive (with expect_tx) by the filling warp
         }
@@ -102,6 +104,7 @@ __device__ __forceinline__ void nm_gemm_ffma_body(const GemmArgs& g, const CUten
         mbar_init_fence();
     }
     __syncthreads();
+    grid_dependency_wait();                                // everything above overlapped the tail of the kernel ahead
 
     const int qs_shift = g.qs_shift;                       // log2(vectors per packed index block)
     const int layout_shift = qs_shift + 5;                 // log2(columns per packed index block)
@@ -270,6 +273,7 @@ __device__ __forceinline__ void nm_gemm_ffma_body(const GemmArgs& g, const CUten
             if (++s == STAGES) { s = 0; ++use; }
         }
         __syncthreads();
+        if (cu + piece_n >= u_end) grid_launch_dependents();   // last piece: only stores are left
         if (lds_volatile_s32(abort_word) != 0) {           // a bounded wait gave up somewhere in the CTA
             if (tid == 0) atomicMax(g.status, kDevTimeoutFull);
             break;
@@ -409,10 +413,9 @@ cudaError_t launch_ffma(const GemmArgs& a, const GemmOutputs& outs, int grid, cu
     e = encode_tensor_map_2d(&map_b, a.B, a.N, a.W, NS, WS - (g_test_short_fill ? 1 : 0));
     if (e != cudaSuccess) return e;
     if (MULTI)
-        nm_gemm_ffma_multi_kernel<MS, NS, WM, WS, KS_, MODE><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(a, map_a, map_b, outs);
-    else
-        nm_gemm_ffma_kernel<MS, NS, WM, WS, KS_, MODE><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(a, map_a, map_b);
-    return cudaGetLastError();
+        return launch_overlapped(nm_gemm_ffma_multi_kernel<MS, NS, WM, WS, KS_, MODE>, grid, Cfg::THREADS, Cfg::SMEM_BYTES, st,
+                                 a, map_a, map_b, outs);
+    return launch_overlapped(nm_gemm_ffma_kernel<MS, NS, WM, WS, KS_, MODE>, grid, Cfg::THREADS, Cfg::SMEM_BYTES, st, a, map_a, map_b);
 }
 
 #define NMSPMM_FFMA_VARIANT(ID, NKEEP, MS, NS, WM, WS, KS, MODE)                                            \
@@ -427,6 +430,8 @@ cudaError_t launch_ffma(const GemmArgs& a, const GemmOutputs& outs, int grid, cu
     NMSPMM_FFMA_VARIANT(kTile64x128, NKEEP, 64, 128, 64, WS, KS, MODE),   \
     NMSPMM_FFMA_VARIANT(kTile32x128, NKEEP, 32, 128, 32, WS, KS, MODE),   \
     NMSPMM_FFMA_VARIANT(kTile16x128, NKEEP, 16, 128, 16, WS, KS, MODE),   \
-    NMSPMM_FFMA_VARIANT(kTile128x256, NKEEP, 128, 256, 64, WS, KS, MODE)
+    NMSPMM_FFMA_VARIANT(kTile128x256, NKEEP, 128, 256, 64, WS, KS, MODE), \
+    NMSPMM_FFMA_VARIANT(kTile16x256, NKEEP, 16, 256, 16, WS, KS, MODE),   \
+    NMSPMM_FFMA_VARIANT(kTile32x256, NKEEP, 32, 256, 32, WS, KS, MODE)
 
 }  // namespace nmspmm

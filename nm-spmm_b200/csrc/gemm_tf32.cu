@@ -155,6 +155,8 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
     const int live_vecs = min(QT, (g.N - bj) / 32);        // vectors of the tile that exist
 
     if (tid == 0) {
+        prefetch_tensor_map(&map_a);
+        prefetch_tensor_map(&map_b);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full + s * 8, DIRECT ? 1 : 1 + Cfg::BUILDERS / 32);   // the TMA bytes + the builder warps
             mbar_init(bar_empty + s * 8, DIRECT ? 1 : Cfg::PRODUCT_WARPS);      // the commits behind the step's products
@@ -180,6 +182,7 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = static_cast<uint32_t>(lds_volatile_s32(tmem_word));
+    grid_dependency_wait();                                // everything above overlapped the tail of the kernel ahead
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -376,6 +379,7 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
         TF_T(e_start);
         bool ok = alive && mbar_wait_bounded(bar_acc, 0, abort_word);
         ok = __all_sync(0xffffffffu, ok);
+        grid_launch_dependents();                          // only stores are left
         TF_T(e_go);
         if (ok) {
             tc_fence_after_sync();
@@ -450,8 +454,7 @@ static cudaError_t launch_tf32(const GemmArgs& a, const GemmOutputs& outs, int t
     if (e != cudaSuccess) return e;
     e = encode_tensor_map_blocks32(&map_b, a.B, a.N, a.W, Cfg::WSP - (g_test_short_fill ? 1 : 0), QT);   // (test hook, see kernels.h)
     if (e != cudaSuccess) return e;
-    kernel<<<tiles, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(a, map_a, map_b, outs, a_blocked);
-    return cudaGetLastError();
+    return launch_overlapped(kernel, tiles, Cfg::THREADS, Cfg::SMEM_BYTES, st, a, map_a, map_b, outs, a_blocked);
 }
 
 #define NMSPMM_TF32_VARIANT(NKEEP, KW, MODE, QT, VL)                                                                   \

@@ -64,6 +64,27 @@ cudaError_t launch_reduce_pieces(int tile_id, const GemmArgs& args, const GemmOu
 cudaError_t launch_reduce_slices(int ns, const GemmArgs& args, const GemmOutputs& outs, int first_tile, int n_tiles,
                                  cudaStream_t st);
 
+// Launch with programmatic stream serialisation: the grid may be set up, and its CTAs may run
+// up to their griddepcontrol.wait, while the kernel ahead of it on the stream is still
+// finishing.  Every kernel launched this way executes griddepcontrol.wait before its first
+// access to global memory.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), unsigned blocks, unsigned threads, size_t smem_bytes,
+                                     cudaStream_t st, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 // Test hook (nmspmm_test_short_fill): non-zero makes the multiply launchers encode B's tensor
 // map with a box one row short.  The kernels are unchanged; their stages then never fill.
 extern int g_test_short_fill;

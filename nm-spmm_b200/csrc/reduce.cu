@@ -18,25 +18,12 @@ namespace nmspmm {
 // set up while the multiply still runs and the grid starts as soon as the multiply's last
 // CTA has exited, instead of a launch latency later (these launches follow multiplies that
 // last 15-100 us).  This wait is what orders the reads below after the multiply's writes.
-__device__ __forceinline__ void wait_for_the_multiply()
-{
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-}
+__device__ __forceinline__ void wait_for_the_multiply() { grid_dependency_wait(); }
 
 template <typename... KArgs, typename... Args>
 static cudaError_t launch_after_multiply(void (*kernel)(KArgs...), unsigned blocks, unsigned threads, cudaStream_t st, Args... args)
 {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(blocks);
-    cfg.blockDim = dim3(threads);
-    cfg.dynamicSmemBytes = 0;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kernel, args...);
+    return launch_overlapped(kernel, blocks, threads, 0, st, args...);
 }
 
 // Thread-fragment map of the FFMA kernels' accumulators for a tile MS x NS with warp tile
@@ -119,6 +106,8 @@ cudaError_t launch_reduce_pieces(int tile_id, const GemmArgs& a, const GemmOutpu
     case kTile32x128: return launch_reduce<32, 128, 32>(a, outs, first_tile, n_tiles, st);
     case kTile16x128: return launch_reduce<16, 128, 16>(a, outs, first_tile, n_tiles, st);
     case kTile128x256: return launch_reduce<128, 256, 64>(a, outs, first_tile, n_tiles, st);
+    case kTile16x256: return launch_reduce<16, 256, 16>(a, outs, first_tile, n_tiles, st);
+    case kTile32x256: return launch_reduce<32, 256, 32>(a, outs, first_tile, n_tiles, st);
     default: return cudaErrorInvalidValue;
     }
 }

@@ -16,6 +16,7 @@ import ctypes
 from typing import Optional
 
 _registered = None
+_workspaces = {}        # per device: the operator's scratch (zero when made: the multiply wants its counter block zero)
 
 
 def _torch():
@@ -51,12 +52,14 @@ def register_ops(pkg):
         need = int(lib.nmspmm_gemm_row_major_workspace_bytes(ctypes.byref(d)))
         if need == 0:
             raise pkg.NMSpMMError("nmspmm_gemm_row_major_workspace_bytes", pkg.UNSUPPORTED)
-        ws = torch.empty(need, dtype=torch.uint8, device=x.device)
+        ws = _workspaces.get(x.device)
+        if ws is None or ws.numel() < need:
+            ws = _workspaces[x.device] = torch.zeros(need, dtype=torch.uint8, device=x.device)
         y = torch.empty((M, N), dtype=torch.float32, device=x.device)
         ci = ctypes.c_void_p(column_info.data_ptr()) if column_info is not None else ctypes.c_void_p(0)
         rc = lib.nmspmm_gemm_row_major(ctypes.byref(d), ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(values.data_ptr()),
                                        ctypes.c_void_p(packed.data_ptr()), ci, ctypes.c_void_p(y.data_ptr()),
-                                       ctypes.c_void_p(ws.data_ptr()), need,
+                                       ctypes.c_void_p(ws.data_ptr()), ws.numel(),
                                        ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
         if rc != pkg.OK:
             raise pkg.NMSpMMError("nmspmm_gemm_row_major", rc)

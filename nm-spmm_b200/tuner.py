@@ -18,7 +18,7 @@ from typing import Iterable, List, Sequence, Tuple
 
 Shape = Tuple[int, int, int, int, int, int, int]       # M, N, K, n_keep, format, path, vec_len
 
-FP32_TILES = (1, 2, 3, 4, 5)          # 128x128, 64x128, 32x128, 16x128, 128x256
+FP32_TILES = (1, 2, 3, 4, 5, 6, 7)    # 128x128, 64x128, 32x128, 16x128, 128x256, 16x256, 32x256
 TF32_TILES = (1, 5)
 SPLITS = (0, 1, 2, 4, 8, 16)          # 0 = the library's automatic schedule on that tile
 
@@ -33,7 +33,7 @@ def candidates(pkg, M: int, path: int) -> List[Tuple[int, int]]:
 
 
 def _tile_rows(tile: int) -> int:
-    return {1: 128, 2: 64, 3: 32, 4: 16, 5: 128}[tile]
+    return {1: 128, 2: 64, 3: 32, 4: 16, 5: 128, 6: 16, 7: 32}[tile]
 
 
 def time_candidate(pkg, torch, op, A, Cs, path: int, tile: int, split_k: int, launches: int = 8) -> float:
