@@ -7,6 +7,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #include "kernels.h"
@@ -159,20 +160,40 @@ static int pick_tile(const nmspmm_gemm_desc* d, int sms)
 // table is read once per process from the text file named by NMSPMM_TUNED_PLANS, else
 // from tuned_plans.txt beside the library; nmspmm_tuned_plan_set adds entries at run time.
 struct TunedPlan { int M, N, K, n_keep, format, path, vec_len, tile, split_k; };
-static std::vector<TunedPlan> g_tuned;
+static std::vector<TunedPlan> g_tuned;                     // the entries, and a hash index over them (shape -> position)
+static std::unordered_multimap<uint64_t, int> g_tuned_index;
+static uint64_t tuned_hash(int M, int N, int K, int n_keep, int format, int path, int vec_len)
+{
+    uint64_t h = 0x9E3779B97F4A7C15ull;
+    for (uint64_t v : { static_cast<uint64_t>(M), static_cast<uint64_t>(N), static_cast<uint64_t>(K),
+                        static_cast<uint64_t>(n_keep * 1024 + format * 256 + path * 128 + vec_len) })
+        h = (h ^ v) * 0xBF58476D1CE4E5B9ull + (h >> 29);
+    return h;
+}
 static std::mutex g_tuned_mutex;
 static bool g_tuned_loaded = false;
 
 static int vec_of(int v) { return v == 64 ? 64 : 32; }
 
+static int tuned_find_locked(int M, int N, int K, int n_keep, int format, int path, int vec_len)
+{
+    auto range = g_tuned_index.equal_range(tuned_hash(M, N, K, n_keep, format, path, vec_len));
+    for (auto it = range.first; it != range.second; ++it) {
+        const TunedPlan& e = g_tuned[it->second];
+        if (e.M == M && e.N == N && e.K == K && e.n_keep == n_keep && e.format == format && e.path == path && e.vec_len == vec_len)
+            return it->second;
+    }
+    return -1;
+}
+
 static void tuned_set_locked(const TunedPlan& t)
 {
-    for (TunedPlan& e : g_tuned)
-        if (e.M == t.M && e.N == t.N && e.K == t.K && e.n_keep == t.n_keep && e.format == t.format && e.path == t.path &&
-            e.vec_len == t.vec_len) {
-            e = t;
-            return;
-        }
+    const int at = tuned_find_locked(t.M, t.N, t.K, t.n_keep, t.format, t.path, t.vec_len);
+    if (at >= 0) {
+        g_tuned[at] = t;
+        return;
+    }
+    g_tuned_index.emplace(tuned_hash(t.M, t.N, t.K, t.n_keep, t.format, t.path, t.vec_len), static_cast<int>(g_tuned.size()));
     g_tuned.push_back(t);
 }
 
@@ -217,14 +238,12 @@ static bool tuned_lookup(const nmspmm_gemm_desc* d, int* tile, int* split_k)
 {
     std::lock_guard<std::mutex> lock(g_tuned_mutex);
     tuned_load_default_locked();
-    for (const TunedPlan& e : g_tuned)
-        if (e.M == d->M && e.N == d->N && e.K == d->K && e.n_keep == d->n_keep && e.format == d->format && e.path == d->path &&
-            e.vec_len == vec_of(d->vec_len)) {
-            *tile = e.tile;
-            *split_k = e.split_k;
-            return true;
-        }
-    return false;
+    if (g_tuned.empty()) return false;
+    const int at = tuned_find_locked(d->M, d->N, d->K, d->n_keep, d->format, d->path, vec_of(d->vec_len));
+    if (at < 0) return false;
+    *tile = g_tuned[at].tile;
+    *split_k = g_tuned[at].split_k;
+    return true;
 }
 
 static int make_plan(const nmspmm_gemm_desc* d_in, int sms, Plan* p, bool any_rows = false)
@@ -237,12 +256,13 @@ static int make_plan(const nmspmm_gemm_desc* d_in, int sms, Plan* p, bool any_ro
     if (d_in->tile == 0 && d_in->split_k == 0 && tuned_lookup(d_in, &tuned.tile, &tuned.split_k)) d = &tuned;
     if (sms <= 0) sms = 148;
     if (d->path == NMSPMM_PATH_TF32) {
-        // Tensor-core path: one CTA per tile and K slice.  Tile 128 x 256 with one CTA per
-        // SM is the faster one for the 64-k window formats once it fills the GPU (measured
-        // at 4096^3: 0.233 against 0.266 ms at 8:32, 0.166 against 0.232 ms at 4:32), tile
-        // 128 x 128 with two CTAs per SM for the 32-k window formats (0.360 against 0.424 ms
-        // at 16:32); the caller's tile wins over both.
-        int want_ns = (((d->N + 255) / 256) * ((d->M + 127) / 128) >= sms) ? 256 : 128;
+        // Tensor-core path: one CTA per tile and K slice.  Tile 128 x 256 with one CTA per SM
+        // wherever B is at least that wide: the gather instructions are twice as wide per
+        // fetched window of A (measured at 4096^3, 16:32: 0.250 against 0.268 ms; on the
+        // skinny and deep-K shapes, where K slices fill the SMs either way: 26.6 against 34.3 us
+        // at 16 x 11008 x 4096, 60.4 against 65.8 us at 128 x 1024 x 131072); the caller's tile
+        // wins over this.
+        int want_ns = d->N >= 256 ? 256 : 128;
         if (d->tile == kTile128x256) want_ns = 256;
         if (d->tile == kTile128x128) want_ns = 128;
         // 64-wide vectors: the variants that gather once per 64 columns exist for tile 128 x 256
@@ -928,6 +948,7 @@ int nmspmm_tuned_plan_clear(void)
     std::lock_guard<std::mutex> lock(g_tuned_mutex);
     g_tuned_loaded = true;
     g_tuned.clear();
+    g_tuned_index.clear();
     return NMSPMM_OK;
 }
 

@@ -116,15 +116,15 @@ def test_split_k_fills_the_machine_for_skinny_shapes(pkg):
     # the tensor-core path: slices when the tiles alone leave SMs idle, pieces always in scratch
     tdeep = pkg.make_desc(128, 1024, 131072, 4, 1, 128, path=pkg.PATH_TF32)
     info = pkg.plan(tdeep)
-    assert info.tile_n == 128 and info.split_k == 296 // 8 and info.grid == 8 * info.split_k
-    assert pkg.workspace_bytes(tdeep) == (64 << 10) + info.grid * 128 * 128 * 4      # counter block + one slot per slice
+    assert info.tile_n == 256 and info.split_k == 148 // 4 and info.grid == 4 * info.split_k      # four wide tiles, one CTA per SM
+    assert pkg.workspace_bytes(tdeep) == (64 << 10) + info.grid * 128 * 256 * 4      # counter block + one slot per slice
     # 512 tiles on 148 one-CTA SMs: three whole waves, the 68 tiles of the last one in two slices each
     tbig = pkg.plan(pkg.make_desc(4096, 4096, 4096, 8, 1, 128, path=pkg.PATH_TF32))
     assert tbig.tile_n == 256 and tbig.n_dp == 444 and tbig.split_k == 2 and tbig.grid == 444 + 2 * 68
     tlow = pkg.plan(pkg.make_desc(4096, 4096, 4096, 16, 0, 128, path=pkg.PATH_TF32))
     assert tlow.tile_n == 256 and tlow.n_dp == 444 and tlow.grid == 444 + 2 * 68   # the wide tile for every ratio once it fills the GPU
-    tsmall = pkg.plan(pkg.make_desc(1024, 2048, 4096, 16, 0, 128, path=pkg.PATH_TF32))
-    assert tsmall.tile_n == 128                                                # 64 wide tiles would leave SMs idle: the narrow one
+    tsmall = pkg.plan(pkg.make_desc(1024, 128, 4096, 16, 0, 128, path=pkg.PATH_TF32))
+    assert tsmall.tile_n == 128                                                # B narrower than the wide tile
     texact = pkg.plan(pkg.make_desc(128 * 148, 256, 4096, 8, 1, 128, path=pkg.PATH_TF32))    # exactly one wave: nothing to slice
     assert texact.split_k == 1 and texact.grid == 148 and pkg.workspace_bytes(pkg.make_desc(128 * 148, 256, 4096, 8, 1, 128, path=pkg.PATH_TF32)) == 0
     one = pkg.plan(pkg.make_desc(128, 128, 64, 16, 0, 128, split_k=1))
