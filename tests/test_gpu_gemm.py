@@ -163,6 +163,10 @@ def test_square_4096_full_size(pkg, orc, n_keep):
     sub = np.ascontiguousarray(p.A_km[:, rows])
     want = orc.nm_gemm_f32(sub, p.B_col, p.D_col)
     assert rel_err(C[torch.from_numpy(rows).cuda()].cpu().numpy(), want) <= FP32_TOL
+    # one whole row block of tiles (128 rows x all columns: every column tile, every thread's fragment)
+    blk = np.arange(1920, 2048)
+    want_blk = orc.nm_gemm_f32(np.ascontiguousarray(p.A_km[:, blk]), p.B_col, p.D_col)
+    assert rel_err(C[1920:2048].cpu().numpy(), want_blk) <= FP32_TOL
     A2 = torch.roll(A, 17, dims=1) * 0.5
     C2 = op.matmul(A2)
     C12 = op.matmul(A + A2)
@@ -173,10 +177,10 @@ def test_square_4096_full_size(pkg, orc, n_keep):
 
 def test_llm_linear_full_size(pkg, orc):
     """LLM-linear configuration at full size (K = 4096, N = 11008, 8:32 by per-vector L2
-    magnitude): tokens 16 and 256 against the checker, both paths of the split schedule."""
+    magnitude): tokens 16, 64 and 256 against the checker, both paths of the split schedule."""
     base = pkg.formats.make_llm_linear(256, seed=81)
     op = pkg.NMSpMM.from_problem(base)
-    for tokens in (16, 256):
+    for tokens in (16, 64, 256):
         A_km = np.ascontiguousarray(base.A_km[:, :tokens])
         want = orc.nm_gemm_f32(A_km, base.B_col, base.D_col)
         got = op.matmul(torch.from_numpy(A_km).cuda()).cpu().numpy()

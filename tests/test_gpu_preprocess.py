@@ -101,6 +101,28 @@ def test_prune_device_matches_the_host_generator(pkg, n_keep, vec_len):
     assert np.array_equal(BT.cpu().numpy(), want_BT)
 
 
+@pytest.mark.parametrize("vec_len", [32, 64])
+def test_prune_device_against_an_independent_statement_of_the_rule(pkg, vec_len):
+    """The LLM-linear weight (4096 x 11008, N(0, 0.02^2)) pruned on the GPU, checked against the
+    rule stated from scratch rather than against the package's own generator: per (32-row
+    window, vector) the kept rows are the 8 with the largest FP64 sum of squares, ascending; the
+    values are the weight's own at those rows."""
+    K, N, n_keep = 4096, 11008, 8
+    Bd = pkg.formats.normal(91, 2, K * N, std=0.02).reshape(K, N)
+    BT, DT = pkg.prune_device(torch.from_numpy(Bd).cuda(), n_keep, vec_len)
+    BT, DT = BT.cpu().numpy(), DT.cpu().numpy()
+    nwin, nvec = K // 32, N // vec_len
+    norms = np.square(Bd.astype(np.float64)).reshape(nwin, 32, nvec, vec_len).sum(axis=3)      # (window, row, vector)
+    kept = np.sort(np.argsort(-norms, axis=1, kind="stable")[:, :n_keep, :], axis=1)             # (window, n_keep, vector)
+    # no near-ties at the cut in this weight: the 8th and 9th largest norms differ clearly
+    ranked = -np.sort(-norms, axis=1)
+    assert float(((ranked[:, n_keep - 1] - ranked[:, n_keep]) / ranked[:, n_keep - 1]).min()) > 1e-9
+    want_DT = np.repeat(kept.reshape(nwin * n_keep, nvec), vec_len // 32, axis=1)
+    assert np.array_equal(DT, want_DT)
+    rows = (kept + (np.arange(nwin) * 32)[:, None, None]).reshape(nwin * n_keep, nvec)
+    assert np.array_equal(BT, np.take_along_axis(Bd, np.repeat(rows, vec_len, axis=1), axis=0))
+
+
 def test_from_dense_runs_prune_pack_and_multiply_on_the_device(pkg, orc):
     p = pkg.formats.make_llm_linear(64, N=1408, K=1024, n_keep=8, seed=77)
     Bd = pkg.formats.normal(77, 2, 1024 * 1408, std=0.02).reshape(1024, 1408)

@@ -117,3 +117,48 @@ def test_tf32_vectors_of_64_columns(pkg, orc, n_keep, fmt, M, N, K):
     torch.cuda.synchronize()
     assert pkg.device_status() == 0
     assert rel_err(C.cpu().numpy(), orc.nm_gemm_f64(p.A_km, p.B_col, p.D_col)) <= TF32_TOL
+
+
+def test_tf32_llm_linear_full_size(pkg, orc):
+    """LLM-linear configuration at full size on the tensor-core path, 16 / 64 / 256 tokens."""
+    base = pkg.formats.make_llm_linear(256, seed=81)
+    op = pkg.NMSpMM.from_problem(base)
+    for tokens in (16, 64, 256):
+        A_km = np.ascontiguousarray(base.A_km[:, :tokens])
+        want = orc.nm_gemm_f64(A_km, base.B_col, base.D_col)
+        got = op.matmul(torch.from_numpy(A_km).cuda(), path=pkg.PATH_TF32).cpu().numpy()
+        assert rel_err(got, want) <= TF32_TOL, tokens
+    assert pkg.device_status() == 0
+
+
+def test_tf32_deep_k_full_size(pkg, orc):
+    """Deep-K configuration at full size (A 128 x 131072, B 131072 x 1024, 4:32): 2048 merged
+    windows per tile cut into K slices, added by the reduction kernel."""
+    p = pkg.formats.make_random(128, 1024, 131072, 4, seed=82)
+    want = orc.nm_gemm_f64(p.A_km, p.B_col, p.D_col)
+    got = run(pkg, p)
+    assert rel_err(got, want) <= TF32_TOL
+
+
+def test_tf32_large_sharded_full_size(pkg, orc):
+    """Large configuration at full size (8192 x 28672 x 8192, 8:32, V = 64) on the tensor-core
+    path, gathering once per 64 columns: sampled rows of the whole product and of one rank's slab
+    of a 4-way shard against the FP64 checker; the same product with 32-wide gathers agrees."""
+    M, N, K = 8192, 28672, 8192
+    p = pkg.formats.make_random(M, N, K, 8, seed=83, vec_len=64)
+    A = torch.from_numpy(p.A_km).cuda()
+    op = pkg.NMSpMM.from_problem(p)
+    assert op.vec_len == 64
+    full = op.matmul(A, path=pkg.PATH_TF32)
+    rows = np.array([0, 127, 128, 4095, 4096, 8191])
+    want = orc.nm_gemm_f64(np.ascontiguousarray(p.A_km[:, rows]), p.B_col, p.D_col)
+    assert rel_err(full[torch.from_numpy(rows).cuda()].cpu().numpy(), want) <= TF32_TOL
+    op.vec_len = 32                                            # the same operand read as 32-wide vectors
+    narrow = op.matmul(A, path=pkg.PATH_TF32)
+    assert float((narrow - full).norm() / full.norm()) <= 1e-6
+    del narrow
+    bt, dt, (c0, c1) = pkg.sharding.shard_operands(p.BT, p.DT, 2, 4, 128)
+    slab = pkg.NMSpMM(bt, dt, K, 8, 128, vec_len=64).matmul(A, path=pkg.PATH_TF32)
+    ref = full[:, c0:c1]
+    assert float((slab - ref).norm() / ref.norm()) <= 1e-6
+    assert pkg.device_status() == 0
