@@ -137,8 +137,10 @@ size_t nmspmm_gemm_workspace_bytes(const nmspmm_gemm_desc* desc);
  * are always summed in k order, so the result does not change from run to run: with up to
  * four pieces per tile the last piece to arrive adds them inside the multiply; with more
  * (deep K, few tiles) and for every split on the TF32 path the pieces stay in scratch and a
- * second, small kernel adds them on the same stream.  Asynchronous on `stream`.
- * column_info_dev is NULL for NMSPMM_FORMAT_LOW. */
+ * second, small kernel adds them on the same stream.  Asynchronous on `stream`: NMSPMM_OK
+ * means the launch was queued.  A device-side bounded wait that gives up (see
+ * nmspmm_device_status) is not reported here; poll nmspmm_device_status at a point where the
+ * caller synchronises anyway.  column_info_dev is NULL for NMSPMM_FORMAT_LOW. */
 int nmspmm_gemm(const nmspmm_gemm_desc* desc,
                 const float* A_dev, const float* B_dev, const int* D_dev, const int* column_info_dev,
                 float* C_dev, void* workspace_dev, size_t workspace_bytes, void* stream);

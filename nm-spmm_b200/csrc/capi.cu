@@ -402,22 +402,24 @@ static int sm_count()
 }
 
 // ---- cached scratch for the entry points whose signature has no workspace ---------
+// One buffer per device and host thread: a thread that alternates between GPUs keeps each
+// GPU's buffer (and never frees one device's memory with another device current).
 struct Scratch {
     void* ptr = nullptr;
     size_t bytes = 0;
-    int device = -1;
 };
-static thread_local Scratch tl_scratch;
+static thread_local Scratch tl_scratch[64];
 
-static int scratch_reserve(size_t bytes, void** out)
+static int scratch_reserve(size_t bytes, void** out, size_t* have)
 {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e);
-    Scratch& s = tl_scratch;
-    if (s.device != dev || s.bytes < bytes) {
+    if (dev < 0 || dev >= 64) return NMSPMM_UNSUPPORTED;
+    Scratch& s = tl_scratch[dev];
+    if (s.bytes < bytes) {
         if (s.ptr) {
-            cudaDeviceSynchronize();
+            cudaDeviceSynchronize();                       // launches that still use the old buffer
             cudaFree(s.ptr);
             s.ptr = nullptr;
             s.bytes = 0;
@@ -428,9 +430,9 @@ static int scratch_reserve(size_t bytes, void** out)
         e = cudaMemset(s.ptr, 0, want);
         if (e != cudaSuccess) return cuda_fail(e);
         s.bytes = want;
-        s.device = dev;
     }
     *out = s.ptr;
+    *have = s.bytes;
     return NMSPMM_OK;
 }
 
@@ -444,14 +446,16 @@ struct Arena {
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
     cudaEvent_t fork = nullptr, join = nullptr, in_done[kHostChunks] = {}, mm_done[kHostChunks] = {};
 };
-static thread_local Arena tl_arena;
+static thread_local Arena tl_arena[64];                   // per device, like the cached scratch
 
-static int arena_reserve(size_t bytes, unsigned char** out, cudaStream_t* st)
+static int arena_reserve(size_t bytes, unsigned char** out, cudaStream_t* st, Arena** which)
 {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e);
-    Arena& a = tl_arena;
+    if (dev < 0 || dev >= 64) return NMSPMM_UNSUPPORTED;
+    Arena& a = tl_arena[dev];
+    *which = &a;
     if (a.device != dev || a.bytes < bytes) {
         if (a.ptr) {
             cudaDeviceSynchronize();
@@ -763,11 +767,12 @@ int nmspmm_gemm_with_cached_workspace(const nmspmm_gemm_desc* desc, const float*
 {
     const size_t need = nmspmm_gemm_workspace_bytes(desc);
     void* ws = nullptr;
+    size_t have = 0;
     if (need > 0) {
-        int rc = scratch_reserve(need, &ws);
+        int rc = scratch_reserve(need, &ws, &have);
         if (rc != NMSPMM_OK) return rc;
     }
-    return nmspmm_gemm(desc, A_dev, B_dev, D_dev, column_info_dev, C_dev, ws, ws ? tl_scratch.bytes : 0, stream);
+    return nmspmm_gemm(desc, A_dev, B_dev, D_dev, column_info_dev, C_dev, ws, have, stream);
 }
 
 // ---- the entry point that allocates nothing --------------------------------------
@@ -872,9 +877,10 @@ int nmspmm_gemm_host(const nmspmm_gemm_desc* desc, const float* A_host, const fl
     const size_t ws_b = round256(ws_need);
     unsigned char* base = nullptr;
     cudaStream_t st = nullptr;
-    rc = arena_reserve(a_b + b_b + 2 * d_b + c_b + ci_b + ws_b, &base, &st);
+    Arena* arp = nullptr;
+    rc = arena_reserve(a_b + b_b + 2 * d_b + c_b + ci_b + ws_b, &base, &st, &arp);
     if (rc != NMSPMM_OK) return rc;
-    Arena& ar = tl_arena;
+    Arena& ar = *arp;
     if (stream) st = static_cast<cudaStream_t>(stream);
     float* dA = reinterpret_cast<float*>(base);
     float* dB = reinterpret_cast<float*>(base + a_b);
@@ -968,22 +974,32 @@ int nmspmm_test_short_fill(int enable)
 
 int nmspmm_release_cached(void)
 {
-    cudaDeviceSynchronize();
-    if (tl_scratch.ptr) cudaFree(tl_scratch.ptr);
-    tl_scratch = Scratch();
-    if (tl_arena.ptr) cudaFree(tl_arena.ptr);
-    if (tl_arena.stream) {
-        cudaStreamDestroy(tl_arena.stream);
-        cudaStreamDestroy(tl_arena.copy_in);
-        cudaStreamDestroy(tl_arena.copy_out);
-        cudaEventDestroy(tl_arena.fork);
-        cudaEventDestroy(tl_arena.join);
-        for (int i = 0; i < kHostChunks; ++i) {
-            cudaEventDestroy(tl_arena.in_done[i]);
-            cudaEventDestroy(tl_arena.mm_done[i]);
+    // frees what the calling host thread holds on every device it used
+    int current = 0;
+    cudaGetDevice(&current);
+    for (int dev = 0; dev < 64; ++dev) {
+        Scratch& s = tl_scratch[dev];
+        Arena& a = tl_arena[dev];
+        if (!s.ptr && !a.ptr && !a.stream) continue;
+        cudaSetDevice(dev);
+        cudaDeviceSynchronize();
+        if (s.ptr) cudaFree(s.ptr);
+        s = Scratch();
+        if (a.ptr) cudaFree(a.ptr);
+        if (a.stream) {
+            cudaStreamDestroy(a.stream);
+            cudaStreamDestroy(a.copy_in);
+            cudaStreamDestroy(a.copy_out);
+            cudaEventDestroy(a.fork);
+            cudaEventDestroy(a.join);
+            for (int i = 0; i < kHostChunks; ++i) {
+                cudaEventDestroy(a.in_done[i]);
+                cudaEventDestroy(a.mm_done[i]);
+            }
         }
+        a = Arena();
     }
-    tl_arena = Arena();
+    cudaSetDevice(current);
     return NMSPMM_OK;
 }
 
