@@ -105,6 +105,24 @@ int nmspmm_preprocess_high_host(int* column_info_host, int pruning_M, int prunin
 
 /* ------------------------------------------------------------------ the multiply */
 
+/* CTA tiles compiled into the library (rows x columns of C).  The exact path has all of 1..7;
+ * the TF32 path 128 x 128 and 128 x 256, the latter in two forms: the tensor core gathers the
+ * kept rows of A (every format and ratio), or B is expanded with zeros and the A window is
+ * multiplied whole (32-k formats with 16, 12 or 8 kept rows).  NMSPMM_TILE_128x256 leaves the
+ * form to the library. */
+enum nmspmm_tile_id {
+    NMSPMM_TILE_AUTO = 0,
+    NMSPMM_TILE_128x128 = 1,
+    NMSPMM_TILE_64x128 = 2,
+    NMSPMM_TILE_32x128 = 3,
+    NMSPMM_TILE_16x128 = 4,
+    NMSPMM_TILE_128x256 = 5,
+    NMSPMM_TILE_16x256 = 6,
+    NMSPMM_TILE_32x256 = 7,
+    NMSPMM_TILE_128x256_GATHER = 8,   /* TF32 path only */
+    NMSPMM_TILE_128x256_EXPAND = 9    /* TF32 path only */
+};
+
 typedef struct nmspmm_gemm_desc {
     int M, N, K;
     int n_keep;        /* kept rows per 32-window: 32, 16, 12 (LOW) / 8, 4 (HIGH); LOW also takes 8 */
@@ -112,7 +130,7 @@ typedef struct nmspmm_gemm_desc {
     int layout_ns;     /* Ns the index buffers were packed for: 32, 64 or 128 */
     int path;          /* nmspmm_path */
     int split_k;       /* >=1: that many K slices per tile; 0: the library balances k windows over the SMs */
-    int tile;          /* 0: chosen by the library; otherwise an nmspmm_tile id (testing / tuning) */
+    int tile;          /* 0: chosen by the library; otherwise one of enum nmspmm_tile_id: for testing and tuning */
     int vec_len;       /* 0 or 32: every 32 columns have their own index list (VEC_LEN of the reference,
                           include/NM-SpMM.h:8).  64: the caller promises that the lists of columns 64 v .. 64 v + 31
                           and 64 v + 32 .. 64 v + 63 are equal (a 64-wide vector stored in the reference's format as
@@ -216,7 +234,7 @@ int nmspmm_device_status(int* status_out, int clear);
 
 /* What the library resolved for a description (filled by nmspmm_gemm_plan). */
 typedef struct nmspmm_gemm_plan_info {
-    int tile;          /* nmspmm_tile id */
+    int tile;          /* nmspmm_tile_id */
     int tile_m, tile_n;
     int split_k;       /* explicit: K slices per tile; automatic: ranges per tile of the balanced tail, rounded up */
     int tiles_x, tiles_y;

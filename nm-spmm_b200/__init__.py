@@ -26,6 +26,8 @@ LIB_PATH = os.environ.get("NMSPMM_LIBRARY") or os.path.join(_HERE, "libnmspmm_b2
 
 OK, INVALID_ARGUMENT, UNSUPPORTED, CUDA_ERROR, WORKSPACE_TOO_SMALL, DEVICE_TIMEOUT = range(6)
 PATH_FP32, PATH_TF32 = 0, 1
+(TILE_AUTO, TILE_128x128, TILE_64x128, TILE_32x128, TILE_16x128, TILE_128x256, TILE_16x256, TILE_32x256,
+ TILE_128x256_GATHER, TILE_128x256_EXPAND) = range(10)   # nmspmm_tile_id
 FORMAT_LOW, FORMAT_HIGH = 0, 1
 VEC_LEN = 32
 

@@ -246,6 +246,20 @@ static bool tuned_lookup(const nmspmm_gemm_desc* d, int* tile, int* split_k)
     return true;
 }
 
+static_assert(NMSPMM_TILE_128x128 == kTile128x128 && NMSPMM_TILE_64x128 == kTile64x128 && NMSPMM_TILE_32x128 == kTile32x128 &&
+                  NMSPMM_TILE_16x128 == kTile16x128 && NMSPMM_TILE_128x256 == kTile128x256 && NMSPMM_TILE_16x256 == kTile16x256 &&
+                  NMSPMM_TILE_32x256 == kTile32x256 && NMSPMM_TILE_128x256_GATHER == kTile128x256Gather &&
+                  NMSPMM_TILE_128x256_EXPAND == kTile128x256Expand && NMSPMM_TILE_128x256_EXPAND + 1 == kTileCount,
+              "the public tile ids are the library's");
+
+// Whether the TF32 path should expand B rather than gather A when the caller leaves the choice
+// to the library (32-k formats, tile 128 x 256).
+static bool tf32_expand_pays(const nmspmm_gemm_desc* d)
+{
+    (void)d;
+    return false;
+}
+
 static int make_plan(const nmspmm_gemm_desc* d_in, int sms, Plan* p, bool any_rows = false)
 {
     int mode = 0;
@@ -263,10 +277,21 @@ static int make_plan(const nmspmm_gemm_desc* d_in, int sms, Plan* p, bool any_ro
         // at 16 x 11008 x 4096, 60.4 against 65.8 us at 128 x 1024 x 131072); the caller's tile
         // wins over this.
         int want_ns = d->N >= 256 ? 256 : 128;
-        if (d->tile == kTile128x256) want_ns = 256;
+        if (d->tile == kTile128x256 || d->tile == kTile128x256Gather || d->tile == kTile128x256Expand) want_ns = 256;
         if (d->tile == kTile128x128) want_ns = 128;
+        // Two forms on tile 128 x 256 (gemm_tf32.cu, gemm_tf32_expand.cu).  With B expanded the
+        // tensor core issues 32 / n_keep times the useful work at its fastest instruction
+        // shape; with A gathered, twice the useful work in small instructions.
+        bool expand = (d->tile == kTile128x256Expand);
+        if ((d->tile == kTileAuto || d->tile == kTile128x256) && want_ns == 256 && mode == kModeLow)
+            expand = tf32_expand_pays(d);
+        if (expand) {
+            for (int i = 0; i < kTf32ExpandVariantCount; ++i)
+                if (kTf32ExpandVariants[i].n_keep == d->n_keep && mode == kModeLow) p->tv = &kTf32ExpandVariants[i];
+            if (!p->tv && d->tile == kTile128x256Expand) return NMSPMM_UNSUPPORTED;
+        }
         // 64-wide vectors: the variants that gather once per 64 columns exist for tile 128 x 256
-        if (d->vec_len == 64 && d->tile != kTile128x128)
+        if (d->vec_len == 64 && d->tile != kTile128x128 && !p->tv)
             for (int i = 0; i < kTf32VariantCount; ++i)
                 if (kTf32Variants[i].n_keep == d->n_keep && kTf32Variants[i].mode == mode && kTf32Variants[i].vec_len == 64) {
                     p->tv = &kTf32Variants[i];
@@ -618,7 +643,7 @@ int nmspmm_gemm_plan(const nmspmm_gemm_desc* desc, nmspmm_gemm_plan_info* out)
     Plan p;
     int rc = make_plan(desc, sm_count(), &p);
     if (rc != NMSPMM_OK) return rc;
-    out->tile = p.v ? p.v->tile_id : 0;
+    out->tile = p.v ? p.v->tile_id : (p.tv->ns == 128 ? kTile128x128 : (p.tv->form == 1 ? kTile128x256Expand : kTile128x256));
     out->tile_m = p.v ? p.v->ms : 128;
     out->tile_n = p.v ? p.v->ns : p.tv->ns;
     out->split_k = p.split_k > 0 ? p.split_k

@@ -23,6 +23,8 @@ enum nmspmm_tile {
     kTile128x256 = 5,
     kTile16x256 = 6,      // skinny activations: 1 KB of every B row per CTA, eight warps
     kTile32x256 = 7,
+    kTile128x256Gather = 8,   // TF32 path only: tile 128 x 256, the form that gathers A with the tensor core
+    kTile128x256Expand = 9,   // TF32 path only: tile 128 x 256, the form that expands B with zeros (32-k formats, 16 / 12 / 8 kept)
     kTileCount
 };
 

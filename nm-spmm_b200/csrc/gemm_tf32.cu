@@ -45,6 +45,7 @@
 #include "gemm_args.h"
 #include "kernels.h"
 #include "tcgen05.cuh"
+#include "tf32_epilogue.cuh"
 
 namespace nmspmm {
 
@@ -101,7 +102,7 @@ struct Tf32Cfg {
     static constexpr int NBUF0 = DIRECT ? 1 : (TMEM_COLS - NS) / N1;
     static constexpr int NBUF = NBUF0 > 4 ? 4 : NBUF0;
     static_assert(NBUF >= 1, "no room for a gather result beside the accumulators");
-    static constexpr int EPI_BYTES = 4 * 32 * 144;           // four warps' 32 x 32 transposition patches, rows 144 bytes apart
+    static constexpr int EPI_BYTES = 4 * kTf32PatchBytes;    // four warps' transposition patches
     static_assert(EPI_BYTES <= STAGES * STAGE_BYTES, "the epilogue reuses the stage ring");
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + AUX_BYTES + CTRL_BYTES + 1024;   // + alignment slack
     static constexpr int ACOL0 = NS;                         // first gather-result column
@@ -385,56 +386,8 @@ nm_gemm_tf32_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a,
             tc_fence_after_sync();
             // every MMA has completed, so every TMA copy has landed and been read: the
             // stage ring is free and serves as the transposition patches
-            const uint32_t patch = ring + (warp - FIRST_BUILDER) * (32 * 144);
-            const int r_sub = lane >> 3, c4 = (lane & 7) * 4;     // store phase: 4 rows x 8 float4 per instruction
-            float* const out0 = sliced ? g.partial + static_cast<size_t>(slot) * MS * NS : nullptr;
-            TF_DECL(e_ld = 0, e_sts = 0, e_stg = 0);
-#pragma unroll 1
-            for (int v = 0; v < live_vecs; ++v) {
-                uint32_t acc[32];
-                TF_T(q0);
-                tmem_ld_x32(tmem_addr(tmem, quad * 32, v * 32), acc);
-                tmem_wait_ld();
-                TF_ADD(e_ld, q0);
-                TF_T(q1);
-                __syncwarp();                              // the previous vector's reads of the patch are over
-#pragma unroll
-                for (int x = 0; x < 8; ++x)
-                    sts_f4(patch + lane * 144 + x * 16,
-                           make_float4(__uint_as_float(acc[4 * x]), __uint_as_float(acc[4 * x + 1]),
-                                       __uint_as_float(acc[4 * x + 2]), __uint_as_float(acc[4 * x + 3])));
-                __syncwarp();
-                TF_ADD(e_sts, q1);
-                TF_T(q2);
-#ifndef NMSPMM_TF32_NOSTORE
-                // 4 rows x 128 bytes per warp instruction.  The destination row pointers are
-                // worked out once per vector; the peers' copies (fused all-gather) in a loop of
-                // their own so that the common single-output case is a plain unrolled run of
-                // shared loads and global stores.
-                float* const base = sliced ? out0 + static_cast<size_t>(quad * 32 + r_sub) * NS + v * 32 + c4
-                                           : g.C + static_cast<size_t>(bi + quad * 32 + r_sub) * outs.ldc + outs.col0 + bj + v * 32 + c4;
-                const size_t row_step = sliced ? static_cast<size_t>(NS) : static_cast<size_t>(outs.ldc);
-                const int rows_left = sliced ? 32 : g.M - (bi + quad * 32 + r_sub);     // rows rr < rows_left exist
-                float4 val[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) val[i] = lds_f4(patch + (4 * i + r_sub) * 144 + c4 * 4);
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    if (4 * i < rows_left) *reinterpret_cast<float4*>(base + static_cast<size_t>(4 * i) * row_step) = val[i];
-                if (!sliced && outs.n_out > 1) {
-                    for (int o = 1; o < outs.n_out; ++o) {       // peers' copies of C when gathering
-                        float* const pb = outs.C_more[o - 1] + (base - g.C);
-#pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            if (4 * i < rows_left) *reinterpret_cast<float4*>(pb + static_cast<size_t>(4 * i) * row_step) = val[i];
-                    }
-                }
-#endif
-                TF_ADD(e_stg, q2);
-            }
-#ifdef NMSPMM_TF32_PROFILE
-            if (e == 0) { TF_OUT(10, e_ld); TF_OUT(11, e_sts); TF_OUT(12, e_stg); }
-#endif
+            tf32_store_vectors<NS>(tmem, quad, lane, 0, live_vecs, ring + (warp - FIRST_BUILDER) * kTf32PatchBytes, g, outs, bi, bj,
+                                   sliced, slot);
         } else if (lane == 0) {
             atomicMax(g.status, kDevTimeoutMma);
         }

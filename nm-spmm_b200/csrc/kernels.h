@@ -50,9 +50,12 @@ struct Tf32Variant {
     int vec_len;        // columns that share an index list: 32, or 64 (adjacent equal lists)
     int smem_bytes, stages, threads;
     cudaError_t (*launch)(const GemmArgs&, const GemmOutputs&, int tiles, cudaStream_t st);
+    int form;           // 0: A gathered by the tensor core, 1: B expanded with zeros
 };
 extern const Tf32Variant kTf32Variants[];
 extern const int kTf32VariantCount;
+extern const Tf32Variant kTf32ExpandVariants[];   // the form that expands B with zeros (gemm_tf32_expand.cu)
+extern const int kTf32ExpandVariantCount;
 
 // Adds the pieces the multiply left in scratch (args.counters == nullptr) for the tiles
 // first_tile .. first_tile + n_tiles - 1 of the given CTA tile and writes C.

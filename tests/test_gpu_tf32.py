@@ -162,3 +162,51 @@ def test_tf32_large_sharded_full_size(pkg, orc):
     ref = full[:, c0:c1]
     assert float((slab - ref).norm() / ref.norm()) <= 1e-6
     assert pkg.device_status() == 0
+
+
+# ---------------------------------------------------------------------------- the form that expands B
+
+@pytest.mark.parametrize("n_keep", [16, 12, 8])
+@pytest.mark.parametrize("M,N,K,split_k", [(128, 256, 64, 0), (256, 512, 512, 0), (200, 640, 256, 1), (132, 384, 2048, 0),
+                                           (132, 384, 2048, 3), (1024, 1024, 1024, 0)])
+def test_tf32_expanded_b_form(pkg, orc, n_keep, M, N, K, split_k):
+    """Tile id 9: the A window multiplied whole by B expanded with zeros (32-k formats).  Ragged
+    rows, a last tile with fewer vectors, K slices, and the automatic schedule."""
+    p = pkg.formats.make_random(M, N, K, n_keep, seed=230 + n_keep)
+    op = pkg.NMSpMM.from_problem(p, fmt=0)
+    A = torch.from_numpy(p.A_km).cuda()
+    assert pkg.plan(op.desc(M, path=pkg.PATH_TF32, tile=pkg.TILE_128x256_EXPAND, split_k=split_k)).tile == pkg.TILE_128x256_EXPAND
+    C = op.matmul(A, path=pkg.PATH_TF32, tile=pkg.TILE_128x256_EXPAND, split_k=split_k)
+    assert torch.equal(op.matmul(A, path=pkg.PATH_TF32, tile=pkg.TILE_128x256_EXPAND, split_k=split_k), C)
+    assert pkg.device_status() == 0
+    assert rel_err(C.cpu().numpy(), orc.nm_gemm_f64(p.A_km, p.B_col, p.D_col)) <= TF32_TOL
+
+
+@pytest.mark.parametrize("n_keep", [16, 12, 8])
+def test_tf32_forms_agree_on_an_index_list_with_repeated_rows(pkg, orc, n_keep):
+    """The reference's sum takes a repeated index twice (include/utils.h:82-95).  The gather
+    form does so by construction; the expanding form has to add the two values of B in
+    the row they share."""
+    M, N, K = 256, 512, 1024
+    p = pkg.formats.make_random(M, N, K, n_keep, seed=236)
+    DT = p.DT.copy().reshape(K // 32, n_keep, N // 32)
+    DT[::2, 1, :] = DT[::2, 0, :]
+    DT[1::4, 3, ::3] = DT[1::4, 2, ::3]
+    p.DT[...] = DT.reshape(p.DT.shape)
+    want = orc.nm_gemm_f64(p.A_km, p.B_col, p.D_col)
+    op = pkg.NMSpMM.from_problem(p, fmt=0)
+    A = torch.from_numpy(p.A_km).cuda()
+    for tile in (pkg.TILE_128x256_GATHER, pkg.TILE_128x256_EXPAND):
+        C = op.matmul(A, path=pkg.PATH_TF32, tile=tile)
+        assert pkg.device_status() == 0
+        assert rel_err(C.cpu().numpy(), want) <= TF32_TOL, tile
+
+
+def test_tf32_expanded_b_form_at_4096_cubed(pkg, orc):
+    p = pkg.formats.make_random(4096, 4096, 4096, 16, seed=81)
+    op = pkg.NMSpMM.from_problem(p, fmt=0)
+    A = torch.from_numpy(p.A_km).cuda()
+    C = op.matmul(A, path=pkg.PATH_TF32, tile=pkg.TILE_128x256_EXPAND)
+    exact = op.matmul(A)
+    assert float((C - exact).norm() / exact.norm()) <= TF32_TOL
+    assert pkg.device_status() == 0

@@ -191,3 +191,23 @@ def test_tuned_plan_table_overrides_the_heuristics_and_only_them(pkg, tmp_path):
         pkg.clear_tuned_plans()
     again = pkg.plan(d)
     assert (again.tile_m, again.tile_n, again.split_k) == (base.tile_m, base.tile_n, base.split_k)
+
+
+def test_tf32_forms_are_selected_by_tile_id(pkg):
+    """Tile ids 8 and 9 force the gathering and the expanding form of the TF32 path; the
+    expanding one exists for the 32-k formats only and neither exists on the exact path."""
+    low = pkg.make_desc(512, 1024, 1024, 16, pkg.FORMAT_LOW, 128, pkg.PATH_TF32)
+    for tile, threads in ((pkg.TILE_128x256_GATHER, 256), (pkg.TILE_128x256_EXPAND, 320)):
+        d = pkg.make_desc(512, 1024, 1024, 16, pkg.FORMAT_LOW, 128, pkg.PATH_TF32, 0, tile)
+        info = pkg.plan(d)
+        assert (info.tile_m, info.tile_n, info.threads) == (128, 256, threads)
+    assert pkg.plan(low).tile in (pkg.TILE_128x256, pkg.TILE_128x256_EXPAND)
+    assert pkg.plan(pkg.make_desc(512, 1024, 1024, 16, pkg.FORMAT_LOW, 128, pkg.PATH_TF32, 0, pkg.TILE_128x128)).tile == pkg.TILE_128x128
+    lib = pkg.load_library()
+    high = pkg.make_desc(512, 1024, 1024, 8, pkg.FORMAT_HIGH, 128, pkg.PATH_TF32, 0, pkg.TILE_128x256_EXPAND)
+    assert lib.nmspmm_gemm_workspace_bytes(ctypes.byref(high)) == 0
+    with pytest.raises(pkg.NMSpMMError):
+        pkg.plan(high)
+    for tile in (pkg.TILE_128x256_GATHER, pkg.TILE_128x256_EXPAND):
+        with pytest.raises(pkg.NMSpMMError):
+            pkg.plan(pkg.make_desc(512, 1024, 1024, 16, pkg.FORMAT_LOW, 128, pkg.PATH_FP32, 0, tile))
