@@ -464,6 +464,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     # bound there): with eight ranks copying at once, buffers on the far socket would put the
     # inter-socket link between every GPU and its data.
     saved_affinity = os.sched_getaffinity(0)
+    numa_probe = pkg.gpu_numa_probe(local_rank)
     numa_bound = pkg.bind_host_to_gpu(local_rank)
     hA = torch.empty(p.A_km.shape, dtype=torch.float32).pin_memory().copy_(torch.from_numpy(p.A_km))
     hB = torch.empty(p.BT.shape, dtype=torch.float32).pin_memory().copy_(torch.from_numpy(p.BT))
@@ -482,6 +483,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     link = {"h2d_gbs_min_over_ranks": min_over_ranks(link_gbs(A_sets[0], hA)),
             "d2h_gbs_min_over_ranks": min_over_ranks(link_gbs(hC, C_sets[0])),
             "numa_bound": bool(numa_bound),
+            "numa_probe_rank0": {"bdf": numa_probe["bdf"], "node": numa_probe["node"], "why_not": numa_probe["why_not"]},
             "note": "a 64 MiB pinned buffer copied alone, every rank at the same time; the e2e call moves "
                     "%.0f MB in and %.0f MB out per step" % ((hA.numel() + hB.numel() + hD.numel()) * 4 / 1e6, hC.numel() * 4 / 1e6)}
 

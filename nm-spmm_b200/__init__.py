@@ -394,22 +394,41 @@ def gemm_host(desc: GemmDesc, A_km, BT, DT, C, on_current_stream: bool = False) 
     _check("nmspmm_gemm_host", lib.nmspmm_gemm_host(ctypes.byref(desc), ptr(A_km), ptr(BT), ptr(DT), ptr(C), st))
 
 
-def gpu_numa_cpus(device_index: int):
-    """CPUs of the NUMA node the GPU hangs off (from sysfs), or None when that cannot be read
-    (single-node hosts report node -1)."""
+def gpu_numa_probe(device_index: int) -> dict:
+    """Where the GPU hangs off the host, read from sysfs: ``{"bdf", "node", "cpus", "why_not"}``.
+    ``cpus`` is None (and ``why_not`` says which step gave nothing) on single-node hosts, which
+    report node -1, and where the container hides the PCI tree."""
+    out = {"bdf": None, "node": None, "cpus": None, "why_not": None}
     try:
         pr = _torch().cuda.get_device_properties(device_index)
-        bdf = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
-        node = int(open(f"/sys/bus/pci/devices/{bdf}/numa_node").read())
-        if node < 0:
-            return None
+        out["bdf"] = bdf = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+    except Exception as e:
+        out["why_not"] = f"no PCI address from the device properties ({type(e).__name__})"
+        return out
+    try:
+        out["node"] = node = int(open(f"/sys/bus/pci/devices/{bdf}/numa_node").read())
+    except Exception as e:
+        out["why_not"] = f"/sys/bus/pci/devices/{bdf}/numa_node unreadable ({type(e).__name__})"
+        return out
+    if node < 0:
+        out["why_not"] = "sysfs reports NUMA node -1 for the GPU"
+        return out
+    try:
         cpus = set()
         for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
             lo, _, hi = part.partition("-")
             cpus.update(range(int(lo), int(hi or lo) + 1))
-        return cpus or None
-    except Exception:
-        return None
+        out["cpus"] = cpus or None
+        if not cpus:
+            out["why_not"] = f"node{node} lists no CPUs"
+    except Exception as e:
+        out["why_not"] = f"/sys/devices/system/node/node{node}/cpulist unreadable ({type(e).__name__})"
+    return out
+
+
+def gpu_numa_cpus(device_index: int):
+    """CPUs of the NUMA node the GPU hangs off (from sysfs), or None when that cannot be read."""
+    return gpu_numa_probe(device_index)["cpus"]
 
 
 def bind_host_to_gpu(device_index: int) -> bool:
