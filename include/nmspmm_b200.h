@@ -166,13 +166,31 @@ int nmspmm_gemm(const nmspmm_gemm_desc* desc,
 /* The multiply for activations stored row-major, A[i*K + k] (no counterpart in the reference,
  * whose A is col-major, include/utils.h:34-38; a linear layer's input is not).  A first kernel
  * on `stream` writes the col-major copy (its k rows padded to a multiple of 4 floats, so M
- * may be any positive number here) into the head of the workspace, the multiply follows.
- * C is row-major M x N as everywhere.  The workspace holds that copy and then what
- * nmspmm_gemm needs: ask nmspmm_gemm_row_major_workspace_bytes. */
+ * may be any positive number here) into the workspace, the multiply follows.
+ * C is row-major M x N as everywhere.  The workspace holds what nmspmm_gemm needs (first, so
+ * that the counter block keeps its place when the same workspace serves different M) and then
+ * that copy: ask nmspmm_gemm_row_major_workspace_bytes. */
 size_t nmspmm_gemm_row_major_workspace_bytes(const nmspmm_gemm_desc* desc);
 int nmspmm_gemm_row_major(const nmspmm_gemm_desc* desc,
                           const float* A_rows_dev, const float* B_dev, const int* D_dev, const int* column_info_dev,
                           float* C_dev, void* workspace_dev, size_t workspace_bytes, void* stream);
+
+/* The same with the activations and the result in 16-bit storage (IEEE half or bfloat16; no
+ * counterpart in the reference, which is FP32 throughout, include/NM-SpMM.h:10-31).  x is
+ * M x K row-major, y M x N row-major, both of `dtype`; B stays FP32 (weights kept in 16 bits
+ * are widened once, nmspmm_widen_device, before they are compressed).  Every half and
+ * bfloat16 value is a TF32 value, so on NMSPMM_PATH_TF32 the products of widened operands
+ * are exact and only the FP32 sums and the final rounding of y (to nearest even) separate the
+ * result from the real one; NMSPMM_PATH_FP32 is exact in the same sense.  One kernel widens
+ * and transposes x, the multiply follows, one kernel rounds y; the workspace holds what the
+ * multiply needs and the two FP32 copies. */
+enum nmspmm_dtype { NMSPMM_DTYPE_F32 = 0, NMSPMM_DTYPE_F16 = 1, NMSPMM_DTYPE_BF16 = 2 };
+size_t nmspmm_gemm_row_major_16_workspace_bytes(const nmspmm_gemm_desc* desc);
+int nmspmm_gemm_row_major_16(const nmspmm_gemm_desc* desc, int dtype,
+                             const void* x_rows_dev, const float* B_dev, const int* D_dev, const int* column_info_dev,
+                             void* y_dev, void* workspace_dev, size_t workspace_bytes, void* stream);
+/* n values (n % 4 == 0) of `dtype` at src_dev (8-byte aligned) -> FP32 at dst_dev (16-byte aligned). */
+int nmspmm_widen_device(int dtype, const void* src_dev, float* dst_dev, size_t n, void* stream);
 
 /* The multiply of one rank of a column-sharded B fused with the all-gather of C (no
  * counterpart in the reference, which runs on one GPU).  The rank's problem is

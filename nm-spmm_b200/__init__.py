@@ -29,6 +29,7 @@ PATH_FP32, PATH_TF32 = 0, 1
 (TILE_AUTO, TILE_128x128, TILE_64x128, TILE_32x128, TILE_16x128, TILE_128x256, TILE_16x256, TILE_32x256,
  TILE_128x256_GATHER, TILE_128x256_EXPAND) = range(10)   # nmspmm_tile_id
 FORMAT_LOW, FORMAT_HIGH = 0, 1
+DTYPE_F32, DTYPE_F16, DTYPE_BF16 = 0, 1, 2               # nmspmm_dtype
 VEC_LEN = 32
 
 # Every symbol include/nmspmm_b200.h declares.
@@ -38,7 +39,8 @@ C_ABI_SYMBOLS = (
     "nmspmm_trans_index_host", "nmspmm_preprocess_low_host", "nmspmm_preprocess_high_host",
     "nmspmm_test_short_fill", "nmspmm_tuned_plan_set", "nmspmm_tuned_plan_load", "nmspmm_tuned_plan_clear",
     "nmspmm_tuned_plan_count", "nmspmm_gemm_workspace_bytes", "nmspmm_gemm", "nmspmm_gemm_row_major",
-    "nmspmm_gemm_row_major_workspace_bytes", "nmspmm_gemm_with_cached_workspace", "nmspmm_device_status",
+    "nmspmm_gemm_row_major_workspace_bytes", "nmspmm_gemm_row_major_16", "nmspmm_gemm_row_major_16_workspace_bytes",
+    "nmspmm_widen_device", "nmspmm_gemm_with_cached_workspace", "nmspmm_device_status",
     "nmspmm_gemm_plan", "nmspmm_gemm_host", "nmspmm_release_cached", "nmspmm_measure_ffma_peak",
     "nmspmm_gemm_static_scratch", "nmspmm_gemm_gather", "nmspmm_prune_device",
 )
@@ -96,6 +98,10 @@ def load_library():
     lib.nmspmm_gemm_row_major_workspace_bytes.restype = sz
     lib.nmspmm_gemm_row_major_workspace_bytes.argtypes = [ctypes.POINTER(GemmDesc)]
     lib.nmspmm_gemm_row_major.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp, vp, sz, vp]
+    lib.nmspmm_gemm_row_major_16_workspace_bytes.restype = sz
+    lib.nmspmm_gemm_row_major_16_workspace_bytes.argtypes = [ctypes.POINTER(GemmDesc)]
+    lib.nmspmm_gemm_row_major_16.argtypes = [ctypes.POINTER(GemmDesc), ctypes.c_int, vp, vp, vp, vp, vp, vp, sz, vp]
+    lib.nmspmm_widen_device.argtypes = [ctypes.c_int, vp, vp, sz, vp]
     lib.nmspmm_gemm_with_cached_workspace.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp, vp]
     lib.nmspmm_gemm_static_scratch.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp, vp]
     lib.nmspmm_prune_device.argtypes = [vp, vp, vp, ci, ci, ci, ci, vp]
@@ -446,6 +452,26 @@ def bind_host_to_gpu(device_index: int) -> bool:
     return True
 
 
+def dtype_id(torch_dtype) -> int:
+    """nmspmm_dtype of a torch dtype (float32, float16, bfloat16)."""
+    torch = _torch()
+    try:
+        return {torch.float32: DTYPE_F32, torch.float16: DTYPE_F16, torch.bfloat16: DTYPE_BF16}[torch_dtype]
+    except KeyError:
+        raise NMSpMMError("dtype_id", UNSUPPORTED) from None
+
+
+def widen_device(t):
+    """nmspmm_widen_device: a contiguous float16 / bfloat16 CUDA tensor (numel % 4 == 0) as float32,
+    exactly -- what weights kept in 16 bits go through once, before they are pruned and compressed."""
+    torch = _torch()
+    assert t.is_contiguous()
+    out = torch.empty(t.shape, dtype=torch.float32, device=t.device)
+    _check("nmspmm_widen_device", load_library().nmspmm_widen_device(dtype_id(t.dtype), ctypes.c_void_p(t.data_ptr()),
+                                                                     ctypes.c_void_p(out.data_ptr()), t.numel(), _stream_ptr()))
+    return out
+
+
 def measure_ffma_peak(packed: bool = False) -> float:
     """Sustained FP32 FMA rate of the current GPU in TFLOP/s (register-only kernel);
     ``packed`` selects the two-lane packed FMA of sm_100 instead of scalar FFMA."""
@@ -512,22 +538,30 @@ class NMSpMM:
         return C
 
     def matmul_rows(self, x, path: int = PATH_FP32, split_k: int = 0, tile: int = 0, out=None):
-        """C (M, N) = x . B for ``x`` given row-major as an (M, K) float32 CUDA tensor (any M >= 1):
-        the library transposes on the GPU ahead of the multiply (nmspmm_gemm_row_major)."""
+        """C (M, N) = x . B for ``x`` given row-major as an (M, K) CUDA tensor (any M >= 1): the
+        library transposes on the GPU ahead of the multiply (nmspmm_gemm_row_major).  ``x`` may
+        be float32, or float16 / bfloat16: then the result has that dtype too, the widening is
+        part of the transposition and one pass rounds the result (nmspmm_gemm_row_major_16)."""
         torch = _torch()
         M, K = x.shape
-        assert K == self.K and x.is_contiguous() and x.dtype == torch.float32
+        assert K == self.K and x.is_contiguous()
+        dtype = dtype_id(x.dtype)
+        lib = load_library()
         d = self.desc(M, path, split_k, tile)
-        need = int(load_library().nmspmm_gemm_row_major_workspace_bytes(ctypes.byref(d)))
+        sizer = lib.nmspmm_gemm_row_major_workspace_bytes if dtype == DTYPE_F32 else lib.nmspmm_gemm_row_major_16_workspace_bytes
+        need = int(sizer(ctypes.byref(d)))
         if need == 0:
             raise NMSpMMError("nmspmm_gemm_row_major_workspace_bytes", UNSUPPORTED)
         ws = self._scratch(need)
-        C = torch.empty((M, self.N), dtype=torch.float32, device=x.device) if out is None else out
+        C = torch.empty((M, self.N), dtype=x.dtype, device=x.device) if out is None else out
+        assert C.dtype == x.dtype and C.is_contiguous()
         col = ctypes.c_void_p(self.column_info.data_ptr()) if self.column_info is not None else ctypes.c_void_p(0)
-        _check("nmspmm_gemm_row_major",
-               load_library().nmspmm_gemm_row_major(ctypes.byref(d), ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(self.B.data_ptr()),
-                                                   ctypes.c_void_p(self.D.data_ptr()), col, ctypes.c_void_p(C.data_ptr()),
-                                                   ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr()))
+        ptrs = (ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(self.B.data_ptr()), ctypes.c_void_p(self.D.data_ptr()), col,
+                ctypes.c_void_p(C.data_ptr()), ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr())
+        if dtype == DTYPE_F32:
+            _check("nmspmm_gemm_row_major", lib.nmspmm_gemm_row_major(ctypes.byref(d), *ptrs))
+        else:
+            _check("nmspmm_gemm_row_major_16", lib.nmspmm_gemm_row_major_16(ctypes.byref(d), dtype, *ptrs))
         return C
 
     def matmul_into(self, A, out_ptrs, ldc: int, col0: int, path: int = PATH_FP32, split_k: int = 0, tile: int = 0) -> None:

@@ -738,11 +738,20 @@ static size_t row_major_copy_bytes(const nmspmm_gemm_desc* d)
     return round256(ld * static_cast<size_t>(d->K) * sizeof(float));
 }
 
+// The workspace of the row-major entries starts with what the multiply needs, so that the
+// counter block has one place, and keeps its zeros, whatever M the workspace was last used
+// with; a plan that needs nothing still leaves the block's bytes alone.  The copies follow.
+static size_t row_major_head_bytes(const Plan& p)
+{
+    const size_t own = p.counters_bytes + p.partial_bytes;
+    return own > 0 ? own : kCounterBlock;
+}
+
 size_t nmspmm_gemm_row_major_workspace_bytes(const nmspmm_gemm_desc* desc)
 {
     Plan p;
     if (!desc || make_plan(desc, sm_count(), &p, true) != NMSPMM_OK) return 0;
-    return row_major_copy_bytes(desc) + p.counters_bytes + p.partial_bytes;
+    return row_major_head_bytes(p) + row_major_copy_bytes(desc);
 }
 
 int nmspmm_gemm_row_major(const nmspmm_gemm_desc* desc, const float* A_rows_dev, const float* B_dev, const int* D_dev,
@@ -752,15 +761,64 @@ int nmspmm_gemm_row_major(const nmspmm_gemm_desc* desc, const float* A_rows_dev,
     Plan p;
     int rc = make_plan(desc, sm_count(), &p, true);
     if (rc != NMSPMM_OK) return rc;
-    const size_t copy_bytes = row_major_copy_bytes(desc), own = p.counters_bytes + p.partial_bytes;
-    if (workspace_bytes < copy_bytes + own) return NMSPMM_WORKSPACE_TOO_SMALL;
+    const size_t copy_bytes = row_major_copy_bytes(desc), own = p.counters_bytes + p.partial_bytes, head = row_major_head_bytes(p);
+    if (workspace_bytes < head + copy_bytes) return NMSPMM_WORKSPACE_TOO_SMALL;
     const int ld = (desc->M + 3) / 4 * 4;
-    float* A_cols = static_cast<float*>(workspace_dev);
+    float* A_cols = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace_dev) + head);
     cudaError_t e = launch_transpose_rows(A_rows_dev, A_cols, desc->M, desc->K, ld, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(e);
     float* out[1] = { C_dev };
-    return gemm_launch(desc, A_cols, B_dev, D_dev, column_info_dev, out, 1, desc->N, 0,
-                       own ? static_cast<unsigned char*>(workspace_dev) + copy_bytes : nullptr, own, stream, ld);
+    return gemm_launch(desc, A_cols, B_dev, D_dev, column_info_dev, out, 1, desc->N, 0, own ? workspace_dev : nullptr, own, stream, ld);
+}
+
+// ---- activations and result in 16-bit storage ---------------------------------------------
+static_assert(NMSPMM_DTYPE_F16 == kDtypeF16 && NMSPMM_DTYPE_BF16 == kDtypeBF16, "the public dtype ids are the library's");
+
+static size_t result_copy_bytes(const nmspmm_gemm_desc* d)
+{
+    return round256(static_cast<size_t>(d->M) * d->N * sizeof(float));
+}
+
+size_t nmspmm_gemm_row_major_16_workspace_bytes(const nmspmm_gemm_desc* desc)
+{
+    Plan p;
+    if (!desc || make_plan(desc, sm_count(), &p, true) != NMSPMM_OK) return 0;
+    return row_major_head_bytes(p) + row_major_copy_bytes(desc) + result_copy_bytes(desc);
+}
+
+int nmspmm_gemm_row_major_16(const nmspmm_gemm_desc* desc, int dtype, const void* A_rows_dev, const float* B_dev, const int* D_dev,
+                             const int* column_info_dev, void* C_dev, void* workspace_dev, size_t workspace_bytes, void* stream)
+{
+    if (!desc || !A_rows_dev || !C_dev || !workspace_dev || !aligned16(workspace_dev)) return NMSPMM_INVALID_ARGUMENT;
+    if (dtype != NMSPMM_DTYPE_F16 && dtype != NMSPMM_DTYPE_BF16) return NMSPMM_INVALID_ARGUMENT;
+    if ((reinterpret_cast<uintptr_t>(C_dev) & 7u) != 0) return NMSPMM_INVALID_ARGUMENT;
+    Plan p;
+    int rc = make_plan(desc, sm_count(), &p, true);
+    if (rc != NMSPMM_OK) return rc;
+    const size_t copy_bytes = row_major_copy_bytes(desc), c_bytes = result_copy_bytes(desc);
+    const size_t own = p.counters_bytes + p.partial_bytes, head = row_major_head_bytes(p);
+    if (workspace_bytes < head + copy_bytes + c_bytes) return NMSPMM_WORKSPACE_TOO_SMALL;
+    const int ld = (desc->M + 3) / 4 * 4;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    unsigned char* ws = static_cast<unsigned char*>(workspace_dev);
+    float* A_cols = reinterpret_cast<float*>(ws + head);
+    float* C32 = reinterpret_cast<float*>(ws + head + copy_bytes);
+    cudaError_t e = launch_transpose_rows_16(dtype, A_rows_dev, A_cols, desc->M, desc->K, ld, st);
+    if (e != cudaSuccess) return cuda_fail(e);
+    float* out[1] = { C32 };
+    rc = gemm_launch(desc, A_cols, B_dev, D_dev, column_info_dev, out, 1, desc->N, 0, own ? ws : nullptr, own, stream, ld);
+    if (rc != NMSPMM_OK) return rc;
+    e = launch_narrow(dtype, C32, C_dev, static_cast<size_t>(desc->M) * desc->N, st);
+    return e == cudaSuccess ? NMSPMM_OK : cuda_fail(e);
+}
+
+int nmspmm_widen_device(int dtype, const void* src_dev, float* dst_dev, size_t n, void* stream)
+{
+    if (!src_dev || !dst_dev || n % 4 != 0 || !aligned16(dst_dev) || (reinterpret_cast<uintptr_t>(src_dev) & 7u) != 0)
+        return NMSPMM_INVALID_ARGUMENT;
+    if (dtype != NMSPMM_DTYPE_F16 && dtype != NMSPMM_DTYPE_BF16) return NMSPMM_INVALID_ARGUMENT;
+    cudaError_t e = launch_widen(dtype, src_dev, dst_dev, n, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? NMSPMM_OK : cuda_fail(e);
 }
 
 int nmspmm_gemm_gather(const nmspmm_gemm_desc* desc, const float* A_dev, const float* B_dev, const int* D_dev,

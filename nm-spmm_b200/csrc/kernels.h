@@ -14,6 +14,13 @@ cudaError_t launch_preprocess_high(const int* DT, int* D, int* cinfo, int pm, in
 // in [M][K] row-major -> out [K][ld] (ld >= M, the extra columns zero).
 cudaError_t launch_transpose_rows(const float* in, float* out, int M, int K, int ld, cudaStream_t st);
 
+// 16-bit storage (convert16.cu): the same transposition from half / bfloat16 rows, n floats
+// rounded to 16 bits, n 16-bit values widened (n % 4 == 0).
+enum { kDtypeF32 = 0, kDtypeF16 = 1, kDtypeBF16 = 2 };
+cudaError_t launch_transpose_rows_16(int dtype, const void* in, float* out, int M, int K, int ld, cudaStream_t st);
+cudaError_t launch_narrow(int dtype, const float* in, void* out, size_t n, cudaStream_t st);
+cudaError_t launch_widen(int dtype, const void* in, float* out, size_t n, cudaStream_t st);
+
 // One compiled FFMA kernel variant.
 struct FfmaVariant {
     int tile_id;        // nmspmm_tile
