@@ -260,6 +260,15 @@ static bool tf32_expand_pays(const nmspmm_gemm_desc* d)
     return false;
 }
 
+// Whether the TF32 path should take the warp-level MMA tiles of 16 / 32 / 64 rows when the
+// caller leaves the choice to the library.
+static bool tf32_few_rows_pays(const nmspmm_gemm_desc* d)
+{
+    // 16 x 11008 x 4096, 8:32: 15.4 us against 30.4 us on the 128-row tensor-core tiles (and
+    // 21.8 us on the exact path); 64 rows: 27.5 against 31.1 us.
+    return d->M <= 64;
+}
+
 static int make_plan(const nmspmm_gemm_desc* d_in, int sms, Plan* p, bool any_rows = false)
 {
     int mode = 0;
@@ -276,6 +285,57 @@ static int make_plan(const nmspmm_gemm_desc* d_in, int sms, Plan* p, bool any_ro
         // skinny and deep-K shapes, where K slices fill the SMs either way: 26.6 against 34.3 us
         // at 16 x 11008 x 4096, 60.4 against 65.8 us at 128 x 1024 x 131072); the caller's tile
         // wins over this.
+        // Few rows of A (M <= 64): tiles of 16, 32 or 64 rows on warp-level MMA, K cut into as
+        // many slices as fill the SMs (gemm_tf32_skinny.cu).
+        const bool few_rows_tile = d->tile == kTile16x128 || d->tile == kTile32x128 || d->tile == kTile64x128;
+        if (few_rows_tile || (d->tile == kTileAuto && tf32_few_rows_pays(d))) {
+            const int ms = few_rows_tile ? (d->tile == kTile16x128 ? 16 : (d->tile == kTile32x128 ? 32 : 64))
+                                         : (d->M <= 16 ? 16 : (d->M <= 32 ? 32 : 64));
+            const Tf32Variant* sv = nullptr;
+            for (int i = 0; i < kTf32SkinnyVariantCount; ++i)
+                if (kTf32SkinnyVariants[i].n_keep == d->n_keep && kTf32SkinnyVariants[i].mode == mode && kTf32SkinnyVariants[i].ms == ms)
+                    sv = &kTf32SkinnyVariants[i];
+            if (few_rows_tile && (!sv || d->M > ms)) return NMSPMM_UNSUPPORTED;
+            if (sv && d->M <= ms) {
+                p->tv = sv;
+                p->ws = sv->ws;
+                p->W = d->K / 32 * d->n_keep;
+                if (p->W % p->ws != 0) return NMSPMM_UNSUPPORTED;
+                p->n_win = p->W / p->ws;
+                p->tiles_x = (d->N + 127) / 128;
+                p->tiles_y = 1;
+                p->n_tiles = p->tiles_x;
+                const int least = (p->n_win + kSkinnyMaxWindows - 1) / kSkinnyMaxWindows;     // a CTA's index list holds that many windows
+                long long s = d->split_k;
+                if (s <= 0) {
+                    // One wave, and about five CTAs per two SMs when more would fit: measured at
+                    // 16 x 11008 x 4096 (86 tiles), 8:32: 3 / 4 / 6 / 8 slices 19.4 / 15.4 / 16.5 / 17.8 us.
+                    const int per_sm = (227 * 1024) / (sv->smem_bytes + 1024) > 4 ? 4 : (227 * 1024) / (sv->smem_bytes + 1024);
+                    s = static_cast<long long>(sms) * per_sm / p->n_tiles;
+                    const long long want = (static_cast<long long>(sms) * 5 / 2 + p->n_tiles / 2) / p->n_tiles;
+                    if (s > want) s = want;
+                    if (s > p->n_win / 2) s = p->n_win / 2;        // at least two windows per slice
+                    if (s < least) s = least;
+                } else if (s < least) {
+                    return NMSPMM_UNSUPPORTED;
+                }
+                if (s > p->n_win) s = p->n_win;
+                if (s < 1) s = 1;
+                if (s * p->n_tiles >= (1LL << 30)) return NMSPMM_UNSUPPORTED;
+                p->split_k = static_cast<int>(s);
+                p->n_dp = 0;
+                p->n_virtual = p->grid = static_cast<int>(s * p->n_tiles);
+                if (s > 1) {
+                    p->slots = p->grid;
+                    p->deferred = true;
+                    p->first_split_tile = 0;
+                    p->n_split_tiles = p->n_tiles;
+                    p->counters_bytes = counter_block_bytes(p->n_tiles);   // unused by this path; keeps the slots off the counter block
+                    p->partial_bytes = static_cast<size_t>(p->slots) * ms * 128 * sizeof(float);
+                }
+                return NMSPMM_OK;
+            }
+        }
         int want_ns = d->N >= 256 ? 256 : 128;
         if (d->tile == kTile128x256 || d->tile == kTile128x256Gather || d->tile == kTile128x256Expand) want_ns = 256;
         if (d->tile == kTile128x128) want_ns = 128;
@@ -643,8 +703,10 @@ int nmspmm_gemm_plan(const nmspmm_gemm_desc* desc, nmspmm_gemm_plan_info* out)
     Plan p;
     int rc = make_plan(desc, sm_count(), &p);
     if (rc != NMSPMM_OK) return rc;
-    out->tile = p.v ? p.v->tile_id : (p.tv->ns == 128 ? kTile128x128 : (p.tv->form == 1 ? kTile128x256Expand : kTile128x256));
-    out->tile_m = p.v ? p.v->ms : 128;
+    out->tile = p.v ? p.v->tile_id
+                    : (p.tv->form == 2 ? (p.tv->ms == 16 ? kTile16x128 : (p.tv->ms == 32 ? kTile32x128 : kTile64x128))
+                                       : (p.tv->ns == 128 ? kTile128x128 : (p.tv->form == 1 ? kTile128x256Expand : kTile128x256)));
+    out->tile_m = p.v ? p.v->ms : (p.tv->ms ? p.tv->ms : 128);
     out->tile_n = p.v ? p.v->ns : p.tv->ns;
     out->split_k = p.split_k > 0 ? p.split_k
                                  : (p.n_tiles > p.n_dp ? (p.n_virtual - p.n_dp + p.n_tiles - p.n_dp - 1) / (p.n_tiles - p.n_dp) : 1);
@@ -719,7 +781,8 @@ static int gemm_launch(const nmspmm_gemm_desc* desc, const float* A_dev, const f
     if (e == cudaSuccess && p.v && p.slots > 0 && p.deferred)
         e = launch_reduce_pieces(p.v->tile_id, a, outs, p.first_split_tile, p.n_split_tiles, static_cast<cudaStream_t>(stream));
     if (e == cudaSuccess && p.tv && p.slots > 0)
-        e = launch_reduce_slices(p.tv->ns, a, outs, p.first_split_tile, p.n_split_tiles, static_cast<cudaStream_t>(stream));
+        e = launch_reduce_slices(p.tv->ns, a, outs, p.first_split_tile, p.n_split_tiles, static_cast<cudaStream_t>(stream),
+                                 p.tv->ms ? p.tv->ms : 128);
     return e == cudaSuccess ? NMSPMM_OK : cuda_fail(e);
 }
 

@@ -57,10 +57,14 @@ struct Tf32Variant {
     int vec_len;        // columns that share an index list: 32, or 64 (adjacent equal lists)
     int smem_bytes, stages, threads;
     cudaError_t (*launch)(const GemmArgs&, const GemmOutputs&, int tiles, cudaStream_t st);
-    int form;           // 0: A gathered by the tensor core, 1: B expanded with zeros
+    int form;           // 0: A gathered by the tensor core, 1: B expanded with zeros, 2: warp-level MMA for few rows
+    int ms;             // tile rows when not 128 (form 2: 16, 32 or 64), else 0
 };
 extern const Tf32Variant kTf32Variants[];
 extern const int kTf32VariantCount;
+extern const Tf32Variant kTf32SkinnyVariants[];   // few rows of A, warp-level MMA (gemm_tf32_skinny.cu)
+extern const int kTf32SkinnyVariantCount;
+constexpr int kSkinnyMaxWindows = 24;              // k windows one CTA of that form takes (its resolved index list is in shared memory)
 extern const Tf32Variant kTf32ExpandVariants[];   // the form that expands B with zeros (gemm_tf32_expand.cu)
 extern const int kTf32ExpandVariantCount;
 
@@ -72,7 +76,7 @@ cudaError_t launch_reduce_pieces(int tile_id, const GemmArgs& args, const GemmOu
 // Adds the K slices the tensor-core multiply (tile 128 x ns) left in scratch for the tiles
 // first_tile .. first_tile + n_tiles - 1 (args.sched.split_k slices each) and writes C.
 cudaError_t launch_reduce_slices(int ns, const GemmArgs& args, const GemmOutputs& outs, int first_tile, int n_tiles,
-                                 cudaStream_t st);
+                                 cudaStream_t st, int ms = 128);
 
 // Launch with programmatic stream serialisation: the grid may be set up, and its CTAs may run
 // up to their griddepcontrol.wait, while the kernel ahead of it on the stream is still

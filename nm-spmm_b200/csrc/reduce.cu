@@ -142,12 +142,13 @@ cudaError_t launch_reduce_pieces(int tile_id, const GemmArgs& a, const GemmOutpu
 // flight for tiles of many slices (deep K: every round of loads is a trip to L2); EPT = 4 with
 // four in flight otherwise (fewer CTAs of fewer registers, more of which are resident before
 // the multiply ends: the launch is what costs there).
-template <int NS, int EPT>
+template <int NS, int EPT, int MS = 128>
 __global__ void __launch_bounds__(256) nm_reduce_slices_kernel(const GemmArgs g, const GemmOutputs outs, int first_tile)
 {
-    constexpr int MS = 128, V4 = NS / 4;                   // float4 words per tile row
+    constexpr int V4 = NS / 4;                             // float4 words per tile row; MS = rows of a slot
     constexpr int FLIGHT = (EPT == 1) ? kReduceInFlight : 4;   // loads in flight per thread
     constexpr int CTAS = MS * V4 / (256 * EPT);            // per tile
+    static_assert(CTAS >= 1 && CTAS * 256 * EPT == MS * V4, "whole CTAs per tile");
     const int sliced_tile = blockIdx.x / CTAS, e0 = (blockIdx.x % CTAS) * (256 * EPT) + threadIdx.x;
     const int tile = first_tile + sliced_tile;
     const int ty = tile / g.tiles_x, tx = tile - ty * g.tiles_x;
@@ -176,16 +177,20 @@ __global__ void __launch_bounds__(256) nm_reduce_slices_kernel(const GemmArgs g,
     }
 }
 
-cudaError_t launch_reduce_slices(int ns, const GemmArgs& a, const GemmOutputs& outs, int first_tile, int n_tiles, cudaStream_t st)
+cudaError_t launch_reduce_slices(int ns, const GemmArgs& a, const GemmOutputs& outs, int first_tile, int n_tiles, cudaStream_t st, int ms)
 {
     if (n_tiles <= 0) return cudaSuccess;
     const bool many = a.sched.split_k > kReduceInFlight / 2;
-    if (ns == 256)
+    if (ns == 256 && ms == 128)
         return many ? launch_after_multiply(nm_reduce_slices_kernel<256, 1>, n_tiles * 32, 256, st, a, outs, first_tile)
                     : launch_after_multiply(nm_reduce_slices_kernel<256, 4>, n_tiles * 8, 256, st, a, outs, first_tile);
-    if (ns == 128)
+    if (ns == 128 && ms == 128)
         return many ? launch_after_multiply(nm_reduce_slices_kernel<128, 1>, n_tiles * 16, 256, st, a, outs, first_tile)
                     : launch_after_multiply(nm_reduce_slices_kernel<128, 4>, n_tiles * 4, 256, st, a, outs, first_tile);
+    // the few-row tiles of gemm_tf32_skinny.cu: slots of ms x 128
+    if (ns == 128 && ms == 64) return launch_after_multiply(nm_reduce_slices_kernel<128, 1, 64>, n_tiles * 8, 256, st, a, outs, first_tile);
+    if (ns == 128 && ms == 32) return launch_after_multiply(nm_reduce_slices_kernel<128, 1, 32>, n_tiles * 4, 256, st, a, outs, first_tile);
+    if (ns == 128 && ms == 16) return launch_after_multiply(nm_reduce_slices_kernel<128, 1, 16>, n_tiles * 2, 256, st, a, outs, first_tile);
     return cudaErrorInvalidValue;
 }
 

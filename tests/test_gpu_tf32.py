@@ -210,3 +210,52 @@ def test_tf32_expanded_b_form_at_4096_cubed(pkg, orc):
     exact = op.matmul(A)
     assert float((C - exact).norm() / exact.norm()) <= TF32_TOL
     assert pkg.device_status() == 0
+
+
+# ---------------------------------------------------------------------------- few rows of A (M <= 64)
+
+FEW_ROWS_TILE = {16: 4, 32: 3, 64: 2}        # nmspmm_tile_id of the 16 / 32 / 64 x 128 tiles
+
+
+@pytest.mark.parametrize("n_keep,fmt", [(8, 1), (4, 1), (16, 0), (8, 0)])
+@pytest.mark.parametrize("M,N,K", [(16, 256, 512), (4, 128, 128), (12, 384, 1024), (20, 160, 512), (32, 1024, 2048), (64, 640, 1024),
+                                   (60, 1408, 4096)])
+@pytest.mark.parametrize("split_k", [0, 3])
+def test_tf32_few_rows_tiles(pkg, orc, n_keep, fmt, M, N, K, split_k):
+    """The warp-level MMA tiles for M <= 64: every supported ratio and format, rows short of the
+    tile, a last tile with fewer than four vectors, automatic and explicit K slices; the automatic
+    choice for these shapes is this form."""
+    ms = 16 if M <= 16 else (32 if M <= 32 else 64)
+    p = pkg.formats.make_random(M, N, K, n_keep, seed=240 + M)
+    op = pkg.NMSpMM.from_problem(p, fmt=fmt, layout_ns=128 if N % 128 == 0 else 32)
+    A = torch.from_numpy(p.A_km).cuda()
+    want = orc.nm_gemm_f64(p.A_km, p.B_col, p.D_col)
+    d = op.desc(M, path=pkg.PATH_TF32, tile=FEW_ROWS_TILE[ms], split_k=split_k)
+    if split_k and (K // (64 if fmt == 1 else 32)) / split_k > 24:
+        with pytest.raises(pkg.NMSpMMError):              # a slice of more windows than a CTA's index list holds
+            pkg.plan(d)
+        return
+    info = pkg.plan(d)
+    assert (info.tile_m, info.tile_n) == (ms, 128)
+    C = op.matmul(A, path=pkg.PATH_TF32, tile=FEW_ROWS_TILE[ms], split_k=split_k)
+    assert torch.equal(op.matmul(A, path=pkg.PATH_TF32, tile=FEW_ROWS_TILE[ms], split_k=split_k), C)
+    assert pkg.device_status() == 0
+    assert rel_err(C.cpu().numpy(), want) <= TF32_TOL
+    auto = pkg.plan(op.desc(M, path=pkg.PATH_TF32))
+    assert (auto.tile_m, auto.tile_n) == (ms, 128)
+
+
+def test_tf32_few_rows_refuses_more_rows_than_the_tile(pkg):
+    with pytest.raises(pkg.NMSpMMError):
+        pkg.plan(pkg.make_desc(128, 1024, 1024, 8, pkg.FORMAT_HIGH, 128, pkg.PATH_TF32, 0, FEW_ROWS_TILE[64]))
+    assert pkg.plan(pkg.make_desc(128, 1024, 1024, 8, pkg.FORMAT_HIGH, 128, pkg.PATH_TF32)).tile_m == 128
+    assert pkg.plan(pkg.make_desc(16, 1024, 1024, 12, pkg.FORMAT_LOW, 128, pkg.PATH_TF32)).tile_m == 128   # 12:32 has no such tile
+
+
+def test_tf32_few_rows_deep_k(pkg, orc):
+    p = pkg.formats.make_random(64, 256, 32768, 4, seed=247)
+    op = pkg.NMSpMM.from_problem(p)
+    C = op.matmul(torch.from_numpy(p.A_km).cuda(), path=pkg.PATH_TF32)
+    assert pkg.plan(op.desc(64, path=pkg.PATH_TF32)).tile_m == 64
+    assert pkg.device_status() == 0
+    assert rel_err(C.cpu().numpy(), orc.nm_gemm_f64(p.A_km, p.B_col, p.D_col)) <= TF32_TOL

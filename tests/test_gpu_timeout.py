@@ -12,15 +12,16 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("path,tile,fmt", [(0, 0, 1), (1, 0, 1), (1, 9, 0)])
-def test_a_wait_that_runs_out_is_reported_and_leaves_the_library_usable(pkg, orc, path, tile, fmt):
-    """Exact path, TF32 gather form, TF32 form that expands B (tile id 9)."""
-    p = pkg.formats.make_random(128, 256, 512, 8, seed=300)
+@pytest.mark.parametrize("path,tile,fmt,rows", [(0, 0, 1, 128), (1, 5, 1, 128), (1, 9, 0, 128), (1, 2, 1, 64)])
+def test_a_wait_that_runs_out_is_reported_and_leaves_the_library_usable(pkg, orc, path, tile, fmt, rows):
+    """Exact path, TF32 gather form, TF32 form that expands B (tile id 9), TF32 few-rows form
+    (tile id 2, at most 64 rows)."""
+    p = pkg.formats.make_random(rows, 256, 512, 8, seed=300)
     op = pkg.NMSpMM.from_problem(p, fmt=fmt)
     A = torch.from_numpy(p.A_km).cuda()
     want = orc.nm_gemm_f64(p.A_km, p.B_col, p.D_col)
     assert pkg.device_status() == 0
-    C = torch.full((128, 256), 7.0, device="cuda")
+    C = torch.full((rows, 256), 7.0, device="cuda")
     assert pkg.test_short_fill(True) == 0
     try:
         op.matmul(A, path=path, tile=tile, out=C, split_k=2)       # two slices per tile: scratch and counters are in play
