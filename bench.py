@@ -619,7 +619,8 @@ WORKLOADS = {
 }
 
 
-def measure_workload(pkg, torch, name: str, tile: int = 0, split_k: int = 0, steps: int = 50, quick: bool = False) -> dict:
+def measure_workload(pkg, torch, name: str, tile: int = 0, split_k: int = 0, steps: int = 50, quick: bool = False,
+                     paths=("fp32", "tf32")) -> dict:
     """One of the other named configurations on one GPU: per-launch device time with the
     operands cycled so that no launch finds them in L2 (these shapes are small enough to live
     there otherwise), the index packing timed alone, the roofline fraction of each path, and
@@ -680,6 +681,8 @@ def measure_workload(pkg, torch, name: str, tile: int = 0, split_k: int = 0, ste
                  f"{reps} launches replayed from a CUDA graph"}
     rows = sorted(set(int(r) for r in np.linspace(0, M - 1, min(M, 16)).astype(np.int64)))
     for pname, path, peak in (("fp32", pkg.PATH_FP32, fp32_peak), ("tf32", pkg.PATH_TF32, tf32_peak)):
+        if pname not in paths:
+            continue
         fns = [lambda o=o, c=c: o.matmul(A, out=c, path=path, tile=tile, split_k=split_k) for o, c in zip(ops, Cs)]
         ms = graph_time(fns)
         plan = pkg.plan(ops[0].desc(M, path=path, tile=tile, split_k=split_k))

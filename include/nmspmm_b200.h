@@ -109,7 +109,9 @@ int nmspmm_preprocess_high_host(int* column_info_host, int pruning_M, int prunin
  * the TF32 path 128 x 128 and 128 x 256, the latter in two forms: the tensor core gathers the
  * kept rows of A (every format and ratio), or B is expanded with zeros and the A window is
  * multiplied whole (32-k formats with 16, 12 or 8 kept rows).  NMSPMM_TILE_128x256 leaves the
- * form to the library. */
+ * form to the library.  On the TF32 path ids 4 / 3 / 2 are streaming tiles of 16 / 32 / 64 rows on
+ * warp-level MMA for M <= 16 / 32 / 64 (K in slices; 8:32 and 4:32 on the 64-k format, 16:32 and
+ * 8:32 on the 32-k format), which the library takes by itself for such M. */
 enum nmspmm_tile_id {
     NMSPMM_TILE_AUTO = 0,
     NMSPMM_TILE_128x128 = 1,

@@ -85,7 +85,7 @@ static int device_info(DeviceInfo** out)
 // ---- plan -----------------------------------------------------------------------
 struct Plan {
     const FfmaVariant* v = nullptr;
-    const Tf32Variant* tv = nullptr;   // set instead of v on the tensor-core path
+    const SlicedVariant* tv = nullptr;   // set instead of v on the tensor-core path and for the few-rows kernels of both paths
     int W = 0, ws = 0, n_win = 0;
     int tiles_x = 0, tiles_y = 0, n_tiles = 0;
     int split_k = 0;        // > 0 explicit slices per tile, 0 automatic
@@ -260,6 +260,60 @@ static bool tf32_expand_pays(const nmspmm_gemm_desc* d)
     return false;
 }
 
+// Rows of the few-rows tile that holds M rows (M <= 64).
+static int few_rows_tile_rows(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : 64); }
+
+// Plan of the few-rows kernels (gemm_tf32_few_rows.cu; `table` = their variants): one row of
+// ms x 128 tiles, every tile cut into the same number of K slices, slices in scratch slots of
+// ms x 128 floats.  NMSPMM_UNSUPPORTED when the ratio / format has no such variant, M does not
+// fit the tile, or an explicit split leaves a slice more windows than a CTA's index list holds.
+static int plan_few_rows(const nmspmm_gemm_desc* d, int mode, int sms, const SlicedVariant* table, int ms, Plan* p)
+{
+    const SlicedVariant* sv = nullptr;
+    for (int i = 0; i < kFewRowsVariantCount; ++i)
+        if (table[i].n_keep == d->n_keep && table[i].mode == mode && table[i].ms == ms) sv = &table[i];
+    if (!sv || d->M > ms) return NMSPMM_UNSUPPORTED;
+    const int W = d->K / 32 * d->n_keep;
+    if (W % sv->ws != 0) return NMSPMM_UNSUPPORTED;
+    const int n_win = W / sv->ws, n_tiles = (d->N + 127) / 128;
+    const int least = (n_win + kFewRowsMaxWindows - 1) / kFewRowsMaxWindows;
+    long long s = d->split_k;
+    if (s <= 0) {
+        // One wave, and about five CTAs per two SMs when more would fit: measured at
+        // 16 x 11008 x 4096 (86 tiles), 8:32, TF32: 3 / 4 / 6 / 8 slices 19.4 / 15.4 / 16.5 / 17.8 us.
+        const int per_sm = (227 * 1024) / (sv->smem_bytes + 1024) > 4 ? 4 : (227 * 1024) / (sv->smem_bytes + 1024);
+        s = static_cast<long long>(sms) * per_sm / n_tiles;
+        const long long want = (static_cast<long long>(sms) * 5 / 2 + n_tiles / 2) / n_tiles;
+        if (s > want) s = want;
+        if (s > n_win / 2) s = n_win / 2;                  // at least two windows per slice
+        if (s < least) s = least;
+    } else if (s < least) {
+        return NMSPMM_UNSUPPORTED;
+    }
+    if (s > n_win) s = n_win;
+    if (s < 1) s = 1;
+    if (s * n_tiles >= (1LL << 30)) return NMSPMM_UNSUPPORTED;
+    p->v = nullptr;
+    p->tv = sv;
+    p->ws = sv->ws;
+    p->W = W;
+    p->n_win = n_win;
+    p->tiles_x = p->n_tiles = n_tiles;
+    p->tiles_y = 1;
+    p->split_k = static_cast<int>(s);
+    p->n_dp = 0;
+    p->n_virtual = p->grid = static_cast<int>(s * n_tiles);
+    if (s > 1) {
+        p->slots = p->grid;
+        p->deferred = true;
+        p->first_split_tile = 0;
+        p->n_split_tiles = n_tiles;
+        p->counters_bytes = counter_block_bytes(n_tiles);      // unused by these kernels; keeps the slots off the counter block
+        p->partial_bytes = static_cast<size_t>(p->slots) * ms * 128 * sizeof(float);
+    }
+    return NMSPMM_OK;
+}
+
 // Whether the TF32 path should take the warp-level MMA tiles of 16 / 32 / 64 rows when the
 // caller leaves the choice to the library.
 static bool tf32_few_rows_pays(const nmspmm_gemm_desc* d)
@@ -285,56 +339,12 @@ static int make_plan(const nmspmm_gemm_desc* d_in, int sms, Plan* p, bool any_ro
         // skinny and deep-K shapes, where K slices fill the SMs either way: 26.6 against 34.3 us
         // at 16 x 11008 x 4096, 60.4 against 65.8 us at 128 x 1024 x 131072); the caller's tile
         // wins over this.
-        // Few rows of A (M <= 64): tiles of 16, 32 or 64 rows on warp-level MMA, K cut into as
-        // many slices as fill the SMs (gemm_tf32_skinny.cu).
+        // Few rows of A (M <= 64): tiles of 16, 32 or 64 rows on warp-level MMA (gemm_tf32_few_rows.cu).
         const bool few_rows_tile = d->tile == kTile16x128 || d->tile == kTile32x128 || d->tile == kTile64x128;
         if (few_rows_tile || (d->tile == kTileAuto && tf32_few_rows_pays(d))) {
-            const int ms = few_rows_tile ? (d->tile == kTile16x128 ? 16 : (d->tile == kTile32x128 ? 32 : 64))
-                                         : (d->M <= 16 ? 16 : (d->M <= 32 ? 32 : 64));
-            const Tf32Variant* sv = nullptr;
-            for (int i = 0; i < kTf32SkinnyVariantCount; ++i)
-                if (kTf32SkinnyVariants[i].n_keep == d->n_keep && kTf32SkinnyVariants[i].mode == mode && kTf32SkinnyVariants[i].ms == ms)
-                    sv = &kTf32SkinnyVariants[i];
-            if (few_rows_tile && (!sv || d->M > ms)) return NMSPMM_UNSUPPORTED;
-            if (sv && d->M <= ms) {
-                p->tv = sv;
-                p->ws = sv->ws;
-                p->W = d->K / 32 * d->n_keep;
-                if (p->W % p->ws != 0) return NMSPMM_UNSUPPORTED;
-                p->n_win = p->W / p->ws;
-                p->tiles_x = (d->N + 127) / 128;
-                p->tiles_y = 1;
-                p->n_tiles = p->tiles_x;
-                const int least = (p->n_win + kSkinnyMaxWindows - 1) / kSkinnyMaxWindows;     // a CTA's index list holds that many windows
-                long long s = d->split_k;
-                if (s <= 0) {
-                    // One wave, and about five CTAs per two SMs when more would fit: measured at
-                    // 16 x 11008 x 4096 (86 tiles), 8:32: 3 / 4 / 6 / 8 slices 19.4 / 15.4 / 16.5 / 17.8 us.
-                    const int per_sm = (227 * 1024) / (sv->smem_bytes + 1024) > 4 ? 4 : (227 * 1024) / (sv->smem_bytes + 1024);
-                    s = static_cast<long long>(sms) * per_sm / p->n_tiles;
-                    const long long want = (static_cast<long long>(sms) * 5 / 2 + p->n_tiles / 2) / p->n_tiles;
-                    if (s > want) s = want;
-                    if (s > p->n_win / 2) s = p->n_win / 2;        // at least two windows per slice
-                    if (s < least) s = least;
-                } else if (s < least) {
-                    return NMSPMM_UNSUPPORTED;
-                }
-                if (s > p->n_win) s = p->n_win;
-                if (s < 1) s = 1;
-                if (s * p->n_tiles >= (1LL << 30)) return NMSPMM_UNSUPPORTED;
-                p->split_k = static_cast<int>(s);
-                p->n_dp = 0;
-                p->n_virtual = p->grid = static_cast<int>(s * p->n_tiles);
-                if (s > 1) {
-                    p->slots = p->grid;
-                    p->deferred = true;
-                    p->first_split_tile = 0;
-                    p->n_split_tiles = p->n_tiles;
-                    p->counters_bytes = counter_block_bytes(p->n_tiles);   // unused by this path; keeps the slots off the counter block
-                    p->partial_bytes = static_cast<size_t>(p->slots) * ms * 128 * sizeof(float);
-                }
-                return NMSPMM_OK;
-            }
+            const int ms = few_rows_tile ? (d->tile == kTile16x128 ? 16 : (d->tile == kTile32x128 ? 32 : 64)) : few_rows_tile_rows(d->M);
+            const int rc_few = plan_few_rows(d, mode, sms, kTf32FewRowsVariants, ms, p);
+            if (rc_few == NMSPMM_OK || few_rows_tile) return rc_few;
         }
         int want_ns = d->N >= 256 ? 256 : 128;
         if (d->tile == kTile128x256 || d->tile == kTile128x256Gather || d->tile == kTile128x256Expand) want_ns = 256;
@@ -352,15 +362,15 @@ static int make_plan(const nmspmm_gemm_desc* d_in, int sms, Plan* p, bool any_ro
         }
         // 64-wide vectors: the variants that gather once per 64 columns exist for tile 128 x 256
         if (d->vec_len == 64 && d->tile != kTile128x128 && !p->tv)
-            for (int i = 0; i < kTf32VariantCount; ++i)
-                if (kTf32Variants[i].n_keep == d->n_keep && kTf32Variants[i].mode == mode && kTf32Variants[i].vec_len == 64) {
-                    p->tv = &kTf32Variants[i];
+            for (int i = 0; i < kSlicedVariantCount; ++i)
+                if (kSlicedVariants[i].n_keep == d->n_keep && kSlicedVariants[i].mode == mode && kSlicedVariants[i].vec_len == 64) {
+                    p->tv = &kSlicedVariants[i];
                     want_ns = p->tv->ns;
                 }
-        for (int i = 0; i < kTf32VariantCount && !p->tv; ++i)
-            if (kTf32Variants[i].n_keep == d->n_keep && kTf32Variants[i].mode == mode && kTf32Variants[i].vec_len == 32 &&
-                kTf32Variants[i].ns == want_ns)
-                p->tv = &kTf32Variants[i];
+        for (int i = 0; i < kSlicedVariantCount && !p->tv; ++i)
+            if (kSlicedVariants[i].n_keep == d->n_keep && kSlicedVariants[i].mode == mode && kSlicedVariants[i].vec_len == 32 &&
+                kSlicedVariants[i].ns == want_ns)
+                p->tv = &kSlicedVariants[i];
         if (!p->tv) return NMSPMM_UNSUPPORTED;
         p->ws = p->tv->ws;
         p->W = d->K / 32 * d->n_keep;

@@ -322,7 +322,7 @@ static cudaError_t launch_tf32_expand(const GemmArgs& a, const GemmOutputs& outs
     { NKEEP, Tf32ExpandCfg<NKEEP>::WS, 32, kModeLow, 256, 32, Tf32ExpandCfg<NKEEP>::SMEM_BYTES, Tf32ExpandCfg<NKEEP>::NA,   \
       Tf32ExpandCfg<NKEEP>::THREADS, &launch_tf32_expand<NKEEP>, 1 }
 
-extern const Tf32Variant kTf32ExpandVariants[] = {
+extern const SlicedVariant kTf32ExpandVariants[] = {
     NMSPMM_TF32_EXPAND_VARIANT(16), NMSPMM_TF32_EXPAND_VARIANT(12), NMSPMM_TF32_EXPAND_VARIANT(8),
 };
 extern const int kTf32ExpandVariantCount = sizeof(kTf32ExpandVariants) / sizeof(kTf32ExpandVariants[0]);

@@ -1,29 +1,31 @@
 // TF32 path for few rows of A (M <= 64: the decode and small-batch shapes of a linear layer).
 //
-// The tcgen05 kernels of gemm_tf32.cu work on 128 rows whatever M is, and a k step costs them
-// about 600 cycles of instruction issue: at 16 x 11008 x 4096 that is three times the time HBM
-// needs to deliver B.  These shapes are bound by streaming B once, so the kernel here is built
-// around that stream: tile MS x 128 with MS = 16, 32 or 64, four warps = the tile's four
-// vectors, many K slices so that every SM holds several CTAs with their own TMA rings, and
-// warp-level mma.sync.m16n8k8 (TF32 operands, FP32 accumulators in registers).  A fragment of
-// A is four shared loads at the k rows the vector's index list names -- the gather is the
-// address -- and serves the vector's four n8 blocks; a k8 group costs a warp 4 MS/16 + 8 shared
-// loads and 4 MS/16 instructions where the exact path needs 40 loads and 64 packed FMAs at
-// MS = 16 (and is bound by them, not by HBM).
+// These shapes are bound by streaming B once.  The tcgen05 tiles of gemm_tf32.cu work on 128
+// rows whatever M is and a k step costs them about 600 cycles of instruction issue: three times
+// the HBM time of B at 16 x 11008 x 4096.  Here: tile MS x 128 with MS = 16, 32 or 64, four
+// warps = the tile's four vectors, K cut into slices so that every SM holds a few CTAs with
+// their own TMA rings, and warp-level mma.sync.m16n8k8 (TF32 operands, FP32 accumulators in
+// registers).  A fragment of A is four shared loads at the k rows the vector's index list names
+// -- the gather is the address -- and serves the vector's four n8 blocks: a k8 group costs a
+// warp 4 MS/16 + 8 shared loads and 4 MS/16 instructions.  The operands are FP32 bit patterns
+// of which the tensor core uses the upper 19 bits, as on the tcgen05 path.
+// (The same structure with an exact inner loop -- lane = column, MS accumulators, packed FMA,
+// A by broadcast 16-byte loads -- was built and is slower than the register-tiled kernels of
+// gemm_ffma.cuh at every shape tried, 24.3 against 20.8 us at 16 x 11008 x 4096 and 66 against
+// 42 us at 64 rows: MS / 4 loads per MS / 2 instructions keep it on the load/store pipe.)
 //
-//   * The A window as blocks [KS][32 rows of A] and the B rows of the window as four blocks
-//     [WS][32], both with 32-byte chunks swizzled within 128-byte rows (the fragments of the
-//     four lanes that share a row or column but read different k then fall into different
-//     banks unless their k agree modulo 4), arrive by TMA in a ring of STAGES slots; one
-//     thread refills a slot after the CTA's barrier behind its window.
+//   * The A window ([KS][16] as it lies in memory for 16 rows, else blocks [KS][32 rows of A])
+//     and the B rows of the window as four blocks [WS][32], the blocks with 32-byte chunks
+//     swizzled within 128-byte rows (fragment loads of lanes that read different k then fall
+//     into different banks unless their k agree modulo 4), arrive by TMA in a ring of STAGES
+//     slots; one thread refills a slot after the CTA's barrier behind its window.
 //   * The k of every kept row of the CTA's windows (through column_info on the 64-k formats)
 //     is resolved once, before the loop, into shared memory: a window's arithmetic is far
 //     shorter than a trip to L2.
 //   * K slices of a tile leave their accumulators in scratch slots of MS x 128 floats and
 //     nm_reduce_slices_kernel adds them in k order; a tile computed by one CTA is stored
 //     directly (to every output buffer when the caller gathers).
-// The operands are FP32 bit patterns of which the tensor core uses the upper 19 bits, as on the
-// tcgen05 path.  Every wait is bounded; a wait that gives up raises the device status word.
+// Every wait is bounded; a wait that gives up raises the device status word.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -33,7 +35,7 @@
 namespace nmspmm {
 
 template <int MS_, int WS_, int KS_, int MODE_>
-struct SkinnyCfg {
+struct FewRowsCfg {
     static constexpr int MS = MS_, NS = 128, WS = WS_, KS = KS_, MODE = MODE_;
     static constexpr int THREADS = 128, MB = MS / 16, GROUPS = WS / 8;
     static constexpr bool A_PLAIN = (MS == 16);              // 16 rows: [KS][16] as it lies in memory; else swizzled blocks of 32 rows
@@ -42,7 +44,7 @@ struct SkinnyCfg {
     static constexpr int B_BYTES = 4 * WS * 128;             // [4 vectors][WS][32]
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int STAGES = 4;
-    static constexpr int MAX_WINDOWS = kSkinnyMaxWindows;    // windows of one CTA (the planner cuts K accordingly)
+    static constexpr int MAX_WINDOWS = kFewRowsMaxWindows;   // windows of one CTA (the planner cuts K accordingly)
     static constexpr int K_BYTES = MAX_WINDOWS * 4 * WS * 4; // resolved k of every kept row: [window][vector][WS]
     static constexpr int CTRL_BYTES = 128;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + K_BYTES + CTRL_BYTES + 1024;   // + alignment slack
@@ -60,11 +62,11 @@ __device__ __forceinline__ void mma_tf32_16x8x8(float (&c)[4], const uint32_t (&
 }
 
 template <int MS_, int WS_, int KS_, int MODE_>
-__global__ void __launch_bounds__(128, (SkinnyCfg<MS_, WS_, KS_, MODE_>::MIN_BLOCKS))
-nm_gemm_tf32_skinny_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+__global__ void __launch_bounds__(128, (FewRowsCfg<MS_, WS_, KS_, MODE_>::MIN_BLOCKS))
+nm_gemm_tf32_few_rows_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                            const GemmOutputs outs, const int a_blocked)
 {
-    using Cfg = SkinnyCfg<MS_, WS_, KS_, MODE_>;
+    using Cfg = FewRowsCfg<MS_, WS_, KS_, MODE_>;
     constexpr int MS = Cfg::MS, NS = Cfg::NS, WS = Cfg::WS, KS = Cfg::KS, MB = Cfg::MB, STAGES = Cfg::STAGES;
 
     extern __shared__ unsigned char smem_raw[];
@@ -222,10 +224,10 @@ nm_gemm_tf32_skinny_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap
 }
 
 template <int MS, int WS, int KS, int MODE>
-static cudaError_t launch_skinny(const GemmArgs& a, const GemmOutputs& outs, int ctas, cudaStream_t st)
+static cudaError_t launch_few_rows(const GemmArgs& a, const GemmOutputs& outs, int ctas, cudaStream_t st)
 {
-    using Cfg = SkinnyCfg<MS, WS, KS, MODE>;
-    auto kernel = nm_gemm_tf32_skinny_kernel<MS, WS, KS, MODE>;
+    using Cfg = FewRowsCfg<MS, WS, KS, MODE>;
+    auto kernel = nm_gemm_tf32_few_rows_kernel<MS, WS, KS, MODE>;
     static bool configured[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -248,18 +250,18 @@ static cudaError_t launch_skinny(const GemmArgs& a, const GemmOutputs& outs, int
     return launch_overlapped(kernel, ctas, Cfg::THREADS, Cfg::SMEM_BYTES, st, a, map_a, map_b, outs, a_blocked);
 }
 
-#define NMSPMM_SKINNY_VARIANT(NKEEP, MS, WS, KS, MODE)                                                                   \
-    { NKEEP, WS, KS, MODE, 128, 32, SkinnyCfg<MS, WS, KS, MODE>::SMEM_BYTES, SkinnyCfg<MS, WS, KS, MODE>::STAGES, 128,   \
-      &launch_skinny<MS, WS, KS, MODE>, 2, MS }
+#define NMSPMM_FEW_ROWS_VARIANT(NKEEP, MS, WS, KS, MODE)                                                               \
+    { NKEEP, WS, KS, MODE, 128, 32, FewRowsCfg<MS, WS, KS, MODE>::SMEM_BYTES, FewRowsCfg<MS, WS, KS, MODE>::STAGES, 128, \
+      &launch_few_rows<MS, WS, KS, MODE>, 2, MS }
 
-extern const Tf32Variant kTf32SkinnyVariants[] = {
-    NMSPMM_SKINNY_VARIANT(8, 16, 16, 64, kModeHigh),  NMSPMM_SKINNY_VARIANT(8, 32, 16, 64, kModeHigh),
-    NMSPMM_SKINNY_VARIANT(8, 64, 16, 64, kModeHigh),  NMSPMM_SKINNY_VARIANT(4, 16, 8, 64, kModeHigh),
-    NMSPMM_SKINNY_VARIANT(4, 32, 8, 64, kModeHigh),   NMSPMM_SKINNY_VARIANT(4, 64, 8, 64, kModeHigh),
-    NMSPMM_SKINNY_VARIANT(16, 16, 16, 32, kModeLow),  NMSPMM_SKINNY_VARIANT(16, 32, 16, 32, kModeLow),
-    NMSPMM_SKINNY_VARIANT(16, 64, 16, 32, kModeLow),  NMSPMM_SKINNY_VARIANT(8, 16, 8, 32, kModeLow),
-    NMSPMM_SKINNY_VARIANT(8, 32, 8, 32, kModeLow),    NMSPMM_SKINNY_VARIANT(8, 64, 8, 32, kModeLow),
+extern const SlicedVariant kTf32FewRowsVariants[] = {
+    NMSPMM_FEW_ROWS_VARIANT(8, 16, 16, 64, kModeHigh),  NMSPMM_FEW_ROWS_VARIANT(8, 32, 16, 64, kModeHigh),
+    NMSPMM_FEW_ROWS_VARIANT(8, 64, 16, 64, kModeHigh),  NMSPMM_FEW_ROWS_VARIANT(4, 16, 8, 64, kModeHigh),
+    NMSPMM_FEW_ROWS_VARIANT(4, 32, 8, 64, kModeHigh),   NMSPMM_FEW_ROWS_VARIANT(4, 64, 8, 64, kModeHigh),
+    NMSPMM_FEW_ROWS_VARIANT(16, 16, 16, 32, kModeLow),  NMSPMM_FEW_ROWS_VARIANT(16, 32, 16, 32, kModeLow),
+    NMSPMM_FEW_ROWS_VARIANT(16, 64, 16, 32, kModeLow),  NMSPMM_FEW_ROWS_VARIANT(8, 16, 8, 32, kModeLow),
+    NMSPMM_FEW_ROWS_VARIANT(8, 32, 8, 32, kModeLow),    NMSPMM_FEW_ROWS_VARIANT(8, 64, 8, 32, kModeLow),
 };
-extern const int kTf32SkinnyVariantCount = sizeof(kTf32SkinnyVariants) / sizeof(kTf32SkinnyVariants[0]);
+extern const int kFewRowsVariantCount = sizeof(kTf32FewRowsVariants) / sizeof(kTf32FewRowsVariants[0]);
 
 }  // namespace nmspmm

@@ -48,8 +48,10 @@ cudaError_t encode_tensor_map_2d(CUtensorMap* map, const float* base, int cols, 
 // encode_tensor_map_2d's swizzle128 form.
 cudaError_t encode_tensor_map_blocks32(CUtensorMap* map, const float* base, int cols, int rows, int box_rows, int box_blocks);
 
-// One compiled TF32 tensor-core kernel variant (tile 128 x ns).
-struct Tf32Variant {
+// One compiled variant of the kernels that cut K into whole slices per tile and leave the
+// slices in scratch slots for nm_reduce_slices_kernel: the TF32 tensor-core kernels (tile
+// 128 x ns) and the few-rows kernels (tile ms x 128).
+struct SlicedVariant {
     int n_keep;         // kept rows per 32-k window
     int ws, ks;         // rows of B / of A per step
     int mode;
@@ -57,15 +59,15 @@ struct Tf32Variant {
     int vec_len;        // columns that share an index list: 32, or 64 (adjacent equal lists)
     int smem_bytes, stages, threads;
     cudaError_t (*launch)(const GemmArgs&, const GemmOutputs&, int tiles, cudaStream_t st);
-    int form;           // 0: A gathered by the tensor core, 1: B expanded with zeros, 2: warp-level MMA for few rows
+    int form;           // 0: A gathered by the tensor core, 1: B expanded with zeros, 2: few rows on warp-level MMA
     int ms;             // tile rows when not 128 (form 2: 16, 32 or 64), else 0
 };
-extern const Tf32Variant kTf32Variants[];
-extern const int kTf32VariantCount;
-extern const Tf32Variant kTf32SkinnyVariants[];   // few rows of A, warp-level MMA (gemm_tf32_skinny.cu)
-extern const int kTf32SkinnyVariantCount;
-constexpr int kSkinnyMaxWindows = 24;              // k windows one CTA of that form takes (its resolved index list is in shared memory)
-extern const Tf32Variant kTf32ExpandVariants[];   // the form that expands B with zeros (gemm_tf32_expand.cu)
+extern const SlicedVariant kSlicedVariants[];
+extern const int kSlicedVariantCount;
+extern const SlicedVariant kTf32FewRowsVariants[];  // few rows of A on warp-level MMA (gemm_tf32_few_rows.cu)
+extern const int kFewRowsVariantCount;
+constexpr int kFewRowsMaxWindows = 24;              // k windows one CTA of that form takes (its resolved index list is in shared memory)
+extern const SlicedVariant kTf32ExpandVariants[];   // the form that expands B with zeros (gemm_tf32_expand.cu)
 extern const int kTf32ExpandVariantCount;
 
 // Adds the pieces the multiply left in scratch (args.counters == nullptr) for the tiles
