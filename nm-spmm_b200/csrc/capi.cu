@@ -362,15 +362,15 @@ static int make_plan(const nmspmm_gemm_desc* d_in, int sms, Plan* p, bool any_ro
         }
         // 64-wide vectors: the variants that gather once per 64 columns exist for tile 128 x 256
         if (d->vec_len == 64 && d->tile != kTile128x128 && !p->tv)
-            for (int i = 0; i < kSlicedVariantCount; ++i)
-                if (kSlicedVariants[i].n_keep == d->n_keep && kSlicedVariants[i].mode == mode && kSlicedVariants[i].vec_len == 64) {
-                    p->tv = &kSlicedVariants[i];
+            for (int i = 0; i < kTf32GatherVariantCount; ++i)
+                if (kTf32GatherVariants[i].n_keep == d->n_keep && kTf32GatherVariants[i].mode == mode && kTf32GatherVariants[i].vec_len == 64) {
+                    p->tv = &kTf32GatherVariants[i];
                     want_ns = p->tv->ns;
                 }
-        for (int i = 0; i < kSlicedVariantCount && !p->tv; ++i)
-            if (kSlicedVariants[i].n_keep == d->n_keep && kSlicedVariants[i].mode == mode && kSlicedVariants[i].vec_len == 32 &&
-                kSlicedVariants[i].ns == want_ns)
-                p->tv = &kSlicedVariants[i];
+        for (int i = 0; i < kTf32GatherVariantCount && !p->tv; ++i)
+            if (kTf32GatherVariants[i].n_keep == d->n_keep && kTf32GatherVariants[i].mode == mode && kTf32GatherVariants[i].vec_len == 32 &&
+                kTf32GatherVariants[i].ns == want_ns)
+                p->tv = &kTf32GatherVariants[i];
         if (!p->tv) return NMSPMM_UNSUPPORTED;
         p->ws = p->tv->ws;
         p->W = d->K / 32 * d->n_keep;

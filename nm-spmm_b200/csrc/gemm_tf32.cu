@@ -433,7 +433,7 @@ static cudaError_t launch_tf32(const GemmArgs& a, const GemmOutputs& outs, int t
     { NKEEP, Tf32Cfg<NKEEP, KW, MODE, QT, VL>::WS, KW, MODE, QT * 32, VL, Tf32Cfg<NKEEP, KW, MODE, QT, VL>::SMEM_BYTES,    \
       Tf32Cfg<NKEEP, KW, MODE, QT, VL>::STAGES, Tf32Cfg<NKEEP, KW, MODE, QT, VL>::THREADS, &launch_tf32<NKEEP, KW, MODE, QT, VL> }
 
-extern const SlicedVariant kSlicedVariants[] = {
+extern const SlicedVariant kTf32GatherVariants[] = {
     NMSPMM_TF32_VARIANT(32, 32, kModeLow, 8, 32),  NMSPMM_TF32_VARIANT(32, 32, kModeLow, 4, 32),
     NMSPMM_TF32_VARIANT(16, 32, kModeLow, 8, 32),  NMSPMM_TF32_VARIANT(16, 32, kModeLow, 4, 32),
     NMSPMM_TF32_VARIANT(12, 32, kModeLow, 8, 32),  NMSPMM_TF32_VARIANT(12, 32, kModeLow, 4, 32),
@@ -445,7 +445,7 @@ extern const SlicedVariant kSlicedVariants[] = {
     NMSPMM_TF32_VARIANT(8, 32, kModeLow, 8, 64),   NMSPMM_TF32_VARIANT(8, 32, kModeHigh, 8, 64),
     NMSPMM_TF32_VARIANT(4, 64, kModeHigh, 8, 64),
 };
-extern const int kSlicedVariantCount = sizeof(kSlicedVariants) / sizeof(kSlicedVariants[0]);
+extern const int kTf32GatherVariantCount = sizeof(kTf32GatherVariants) / sizeof(kTf32GatherVariants[0]);
 
 #ifdef NMSPMM_TF32_PROFILE
 // Diagnostic build only: reads and clears the phase counters.

@@ -62,8 +62,8 @@ struct SlicedVariant {
     int form;           // 0: A gathered by the tensor core, 1: B expanded with zeros, 2: few rows on warp-level MMA
     int ms;             // tile rows when not 128 (form 2: 16, 32 or 64), else 0
 };
-extern const SlicedVariant kSlicedVariants[];
-extern const int kSlicedVariantCount;
+extern const SlicedVariant kTf32GatherVariants[];
+extern const int kTf32GatherVariantCount;
 extern const SlicedVariant kTf32FewRowsVariants[];  // few rows of A on warp-level MMA (gemm_tf32_few_rows.cu)
 extern const int kFewRowsVariantCount;
 constexpr int kFewRowsMaxWindows = 24;              // k windows one CTA of that form takes (its resolved index list is in shared memory)
