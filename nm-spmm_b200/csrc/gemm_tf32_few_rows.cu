@@ -43,7 +43,7 @@ struct FewRowsCfg {
     static constexpr int A_BYTES = A_PLAIN ? KS * 64 : ABLK * KS * 128;
     static constexpr int B_BYTES = 4 * WS * 128;             // [4 vectors][WS][32]
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = 4;
+    static constexpr int STAGES = (MS == 16) ? 4 : ((MS == 32) ? 3 : 2);   // four CTAs per SM in every case
     static constexpr int MAX_WINDOWS = kFewRowsMaxWindows;   // windows of one CTA (the planner cuts K accordingly)
     static constexpr int K_BYTES = MAX_WINDOWS * 4 * WS * 4; // resolved k of every kept row: [window][vector][WS]
     static constexpr int CTRL_BYTES = 128;
