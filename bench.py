@@ -691,6 +691,8 @@ def measure_workload(pkg, torch, name: str, tile: int = 0, split_k: int = 0, ste
         out[pname] = {"ms": ms, "useful_tflops": useful / (ms * 1e-3) / 1e12, "bytes_per_s_gbs": abytes / (ms * 1e-3) / 1e9,
                       "roofline_frac": max(useful / peak, abytes / hbm) / (ms * 1e-3),
                       "bound": "hbm" if abytes / hbm > useful / peak else "flops",
+                      "kernel": ("nm_gemm_ffma_kernel" if pname == "fp32" else
+                                 ("nm_gemm_tf32_few_rows_kernel" if plan.tile_m < 128 else "nm_gemm_tf32_kernel")),
                       "tile": [plan.tile_m, plan.tile_n], "ctas": plan.grid, "whole_tiles": plan.n_dp,
                       "rel_err_rows": err, "parity": bool(err <= (1e-5 if pname == "fp32" else 2e-3))}
     assert pkg.device_status() == 0
