@@ -43,7 +43,8 @@ typedef enum nmspmm_status {
 /* Arithmetic of the gathered mini-GEMM. */
 typedef enum nmspmm_path {
     NMSPMM_PATH_FP32 = 0,          /* exact FP32 FFMA, register tiled */
-    NMSPMM_PATH_TF32 = 1           /* tcgen05 kind::tf32, FP32 accumulation in TMEM */
+    NMSPMM_PATH_TF32 = 1           /* TF32 products, FP32 accumulation: tcgen05 kind::tf32 with accumulators in TMEM;
+                                      for M <= 64 warp-level mma.sync tiles of 16 / 32 / 64 rows */
 } nmspmm_path;
 
 /* Index format of D (selected in the reference by which entry point is called). */
