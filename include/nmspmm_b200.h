@@ -306,6 +306,13 @@ int nmspmm_tuned_plan_load(const char* path);                                   
 int nmspmm_tuned_plan_clear(void);
 int nmspmm_tuned_plan_count(void);
 
+/* Tile order of the TF32 path's 128-row tiles (tuning and tests).  -1 (the default, or the value of the
+ * environment variable NMSPMM_TILE_BAND when the library was loaded): the library walks the tiles in bands
+ * of columns when the compressed B is too large to stay in L2 (8192 x 28672 x 8192, 8:32: DRAM reads of
+ * one multiply 12.4 -> 4.0 GB, 4.49 -> 4.15 ms), row by row otherwise.  0: always row by row.  n > 0: bands of
+ * n tile columns wherever there are more columns and at least two rows of tiles.  Returns the previous value. */
+int nmspmm_set_tile_band(int band);
+
 /* ------------------------------------------------------------------ testing
  * Makes the bounded device-side waits run out without faulting or hanging anything: while
  * enabled, the multiply's launchers encode the tensor map of B with a box one row short, so

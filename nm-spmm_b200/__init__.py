@@ -37,7 +37,7 @@ C_ABI_SYMBOLS = (
     "nmspmm_status_string", "nmspmm_last_cuda_error", "nmspmm_version",
     "nmspmm_trans_index_device", "nmspmm_preprocess_low_device", "nmspmm_preprocess_high_device",
     "nmspmm_trans_index_host", "nmspmm_preprocess_low_host", "nmspmm_preprocess_high_host",
-    "nmspmm_test_short_fill", "nmspmm_tuned_plan_set", "nmspmm_tuned_plan_load", "nmspmm_tuned_plan_clear",
+    "nmspmm_test_short_fill", "nmspmm_set_tile_band", "nmspmm_tuned_plan_set", "nmspmm_tuned_plan_load", "nmspmm_tuned_plan_clear",
     "nmspmm_tuned_plan_count", "nmspmm_gemm_workspace_bytes", "nmspmm_gemm", "nmspmm_gemm_row_major",
     "nmspmm_gemm_row_major_workspace_bytes", "nmspmm_gemm_row_major_16", "nmspmm_gemm_row_major_16_workspace_bytes",
     "nmspmm_widen_device", "nmspmm_gemm_with_cached_workspace", "nmspmm_device_status",
@@ -470,6 +470,11 @@ def widen_device(t):
     _check("nmspmm_widen_device", load_library().nmspmm_widen_device(dtype_id(t.dtype), ctypes.c_void_p(t.data_ptr()),
                                                                      ctypes.c_void_p(out.data_ptr()), t.numel(), _stream_ptr()))
     return out
+
+
+def set_tile_band(band: int) -> int:
+    """nmspmm_set_tile_band: -1 automatic, 0 row by row, n bands of n tile columns (TF32 path).  Returns the previous value."""
+    return int(load_library().nmspmm_set_tile_band(int(band)))
 
 
 def measure_ffma_peak(packed: bool = False) -> float:

@@ -88,6 +88,7 @@ struct Plan {
     const SlicedVariant* tv = nullptr;   // set instead of v on the tensor-core path and for the few-rows kernels of both paths
     int W = 0, ws = 0, n_win = 0;
     int tiles_x = 0, tiles_y = 0, n_tiles = 0;
+    int band = 0;           // tile order: columns of tiles per band (gemm_args.h::tile_coords), 0 = row by row
     int split_k = 0;        // > 0 explicit slices per tile, 0 automatic
     int n_dp = 0;           // automatic: leading tiles computed whole
     int n_virtual = 0;      // unit ranges (= CTAs)
@@ -260,6 +261,27 @@ static bool tf32_expand_pays(const nmspmm_gemm_desc* d)
     return false;
 }
 
+static int g_tile_band = getenv("NMSPMM_TILE_BAND") ? atoi(getenv("NMSPMM_TILE_BAND")) : -1;   // see nmspmm_set_tile_band
+
+// Band width of the tile order.  A compressed B that fits L2 comfortably stays there whatever
+// the order.  A larger one (the large sharded configuration on one GPU: 235 MB against 126 MB of
+// L2) would be streamed from HBM once per row of tiles; bands of about 32 MB of B are walked one
+// after the other instead, each over all rows of tiles, and what is re-read per band is A.
+// Tensor-core path only: 8192 x 28672 x 8192 went from 4.49 to 4.15 ms.  The exact path is
+// compute-bound there (B streams at under 1 TB/s), and the extra index arithmetic cost its
+// kernels, which sit at their register limit, 1 - 10 % at 4096^3: they keep the plain order.
+static int tile_band(const nmspmm_gemm_desc* d, int W, int ns, int tiles_x, int tiles_y)
+{
+    const int forced = g_tile_band;                        // measurement / test knob: 0 = never, n = that width, -1 = the rule below
+    if (forced >= 0) return (forced > 0 && forced < tiles_x && tiles_y >= 2) ? (forced > 127 ? 127 : forced) : 0;
+    const double b_bytes = static_cast<double>(W) * d->N * sizeof(float);
+    if (tiles_y < 2 || b_bytes <= 64e6) return 0;
+    int band = static_cast<int>(32e6 / (static_cast<double>(W) * ns * sizeof(float)));
+    if (band < 4) band = 4;
+    if (band > 127) band = 127;
+    return band < tiles_x ? band : 0;
+}
+
 // Rows of the few-rows tile that holds M rows (M <= 64).
 static int few_rows_tile_rows(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : 64); }
 
@@ -381,6 +403,7 @@ static int make_plan(const nmspmm_gemm_desc* d_in, int sms, Plan* p, bool any_ro
         const long long nt = static_cast<long long>(p->tiles_x) * p->tiles_y;
         if (nt >= (1LL << 26)) return NMSPMM_UNSUPPORTED;
         p->n_tiles = static_cast<int>(nt);
+        p->band = tile_band(d, p->W, p->tv->ns, p->tiles_x, p->tiles_y);
         // K slices.  The caller's number applies to every tile.  Otherwise: tiles that fill
         // complete waves of resident CTAs run whole; the tiles of the partial last wave (all
         // tiles of a small problem) are cut into as many slices, of at least four windows,
@@ -766,7 +789,7 @@ static int gemm_launch(const nmspmm_gemm_desc* desc, const float* A_dev, const f
     a.M = desc->M;
     a.N = desc->N;
     a.W = p.W;
-    a.tiles_x = p.tiles_x;
+    a.tiles_x = pack_tiles_x(p.tiles_x, p.band);
     a.sched.n_tiles = p.n_tiles;
     a.sched.n_win = p.n_win;
     a.sched.n_virtual = p.n_virtual;
@@ -1119,6 +1142,13 @@ int nmspmm_tuned_plan_count(void)
     std::lock_guard<std::mutex> lock(g_tuned_mutex);
     tuned_load_default_locked();
     return static_cast<int>(g_tuned.size());
+}
+
+int nmspmm_set_tile_band(int band)
+{
+    const int was = g_tile_band;
+    g_tile_band = band;
+    return was;
 }
 
 int nmspmm_test_short_fill(int enable)

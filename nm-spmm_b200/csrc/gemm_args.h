@@ -51,7 +51,7 @@ struct GemmArgs {
     unsigned* counters;    // one per tile, zero between calls; nullptr: pieces stay in scratch for the reduction kernel
     int* status;           // device status word (0 = ok)
     int M, N, W;
-    int tiles_x;           // tiles per row of tiles
+    int tiles_x;           // tiles per row of tiles, and the band width of the tile order (pack_tiles_x / tile_coords)
     UnitSchedule sched;    // n_tiles, n_win (k windows per tile, W / WS), ranges
     int qs_shift;          // log2 of the vectors per packed index block (layout_ns / 32): 0, 1 or 2
 };
@@ -70,6 +70,29 @@ struct GemmOutputs {
     int lda;               // host side only (tensor-map encoding): floats between consecutive k rows of A; 0 = M
 };
 NMSPMM_HD float* output_of(const GemmArgs& a, const GemmOutputs& o, int i) { return i == 0 ? a.C : o.C_more[i - 1]; }
+
+// Tile order.  GemmArgs::tiles_x carries the tiles per row of tiles in its low 24 bits and a band
+// width in tiles above them.  Band width 0: tiles are numbered row by row.  Otherwise the columns
+// of tiles are cut into bands of that many, the bands are walked one after the other and each
+// band row by row: the CTAs resident at one time then share a band of B that stays in L2 (and a
+// few row panels of A) instead of streaming all of B once per row of tiles.  The planner bands
+// tensor-core problems whose compressed B outgrows L2 (make_plan); the exact path's kernels
+// read the low bits only and number their tiles row by row.
+constexpr int kTileBandShift = 24;
+NMSPMM_HD int pack_tiles_x(int tiles_x, int band) { return tiles_x | (band << kTileBandShift); }
+NMSPMM_HD void tile_coords(int tile, int tiles_x_packed, int tiles_y, int& ty, int& tx)
+{
+    const int tiles_x = tiles_x_packed & ((1 << kTileBandShift) - 1), band = tiles_x_packed >> kTileBandShift;
+    if (band == 0) {
+        ty = tile / tiles_x;
+        tx = tile - ty * tiles_x;
+        return;
+    }
+    const int per_band = band * tiles_y, b = tile / per_band, r = tile - b * per_band;
+    const int x0 = b * band, w = (tiles_x - x0 < band) ? tiles_x - x0 : band;     // the last band may be narrower
+    ty = r / w;
+    tx = x0 + (r - ty * w);
+}
 
 // Which windows (of n_win) slice z of split_k owns: the first n_win % split_k
 // slices get one extra window (the split of src/kernel_64x128_8x8.cu:21-37 of the

@@ -98,7 +98,8 @@ nm_gemm_tf32_expand_kernel(const GemmArgs g, const __grid_constant__ CUtensorMap
     const int n_slices = sliced ? g.sched.split_k : 1;
     const int slot = static_cast<int>(blockIdx.x) - n_dp;
     const int tile = sliced ? n_dp + slot / n_slices : static_cast<int>(blockIdx.x);
-    const int ty = tile / g.tiles_x, tx = tile - ty * g.tiles_x;
+    int ty, tx;
+    tile_coords(tile, g.tiles_x, (g.M + MS - 1) / MS, ty, tx);
     const int bi = ty * MS, bj = tx * NS;
     int win0, n_win;
     slice_range(g.sched.n_win, n_slices, sliced ? slot % n_slices : 0, win0, n_win);

@@ -67,7 +67,7 @@ nm_reduce_pieces_kernel(const GemmArgs g, const GemmOutputs outs, int first_tile
     int v_first, v_last;
     tile_contributors(g.sched, tile, v_first, v_last);
     if (v_first == v_last) return;                         // one range held the whole tile and stored it
-    const int ty = tile / g.tiles_x, tx = tile - ty * g.tiles_x;
+    const int ty = tile / g.tiles_x, tx = tile - ty * g.tiles_x;          // the exact path numbers its tiles row by row
     const int bj = tx * NS, bi = ty * MS;
     const int r = bi + Map::row(tid, i), c = bj + Map::col0(tid) + 16 * half;
     if (Map::vec(tid) * kVecLen >= g.N - bj || r >= g.M) return;       // vectors past N, rows past M
@@ -151,7 +151,8 @@ __global__ void __launch_bounds__(256) nm_reduce_slices_kernel(const GemmArgs g,
     static_assert(CTAS >= 1 && CTAS * 256 * EPT == MS * V4, "whole CTAs per tile");
     const int sliced_tile = blockIdx.x / CTAS, e0 = (blockIdx.x % CTAS) * (256 * EPT) + threadIdx.x;
     const int tile = first_tile + sliced_tile;
-    const int ty = tile / g.tiles_x, tx = tile - ty * g.tiles_x;
+    int ty, tx;
+    tile_coords(tile, g.tiles_x, (g.M + MS - 1) / MS, ty, tx);
     const int bi = ty * MS, bj = tx * NS;
     const int S = g.sched.split_k;
     wait_for_the_multiply();

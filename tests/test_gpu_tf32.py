@@ -259,3 +259,24 @@ def test_tf32_few_rows_deep_k(pkg, orc):
     assert pkg.plan(op.desc(64, path=pkg.PATH_TF32)).tile_m == 64
     assert pkg.device_status() == 0
     assert rel_err(C.cpu().numpy(), orc.nm_gemm_f64(p.A_km, p.B_col, p.D_col)) <= TF32_TOL
+
+
+@pytest.mark.parametrize("n_keep,fmt,tile", [(8, 1, 5), (16, 0, 5), (8, 0, 1), (16, 0, 9)])
+@pytest.mark.parametrize("M,N,K,band,split_k", [(512, 1280, 512, 2, 0), (392, 1024, 1024, 3, 0), (512, 1536, 512, 2, 2), (1024, 4096, 256, 4, 0)])
+def test_tf32_tiles_walked_in_bands_of_columns(pkg, orc, n_keep, fmt, tile, M, N, K, band, split_k):
+    """The tile order the library takes by itself when B outgrows L2, forced here on small shapes:
+    bands of `band` tile columns, the last band narrower, ragged rows, whole tiles and K slices
+    (the reduction kernel has to map tiles the same way).  Same result as row by row, bit for bit."""
+    p = pkg.formats.make_random(M, N, K, n_keep, seed=250 + band)
+    op = pkg.NMSpMM.from_problem(p, fmt=fmt)
+    A = torch.from_numpy(p.A_km).cuda()
+    was = pkg.set_tile_band(0)
+    try:
+        plain = op.matmul(A, path=pkg.PATH_TF32, tile=tile, split_k=split_k)
+        assert pkg.set_tile_band(band) == 0
+        banded = op.matmul(A, path=pkg.PATH_TF32, tile=tile, split_k=split_k)
+    finally:
+        pkg.set_tile_band(was)
+    assert pkg.device_status() == 0
+    assert torch.equal(banded, plain)
+    assert rel_err(banded.cpu().numpy(), orc.nm_gemm_f64(p.A_km, p.B_col, p.D_col)) <= TF32_TOL
