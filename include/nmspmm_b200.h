@@ -315,8 +315,9 @@ int nmspmm_set_tile_band(int band);
 
 /* ------------------------------------------------------------------ testing
  * Makes the bounded device-side waits run out without faulting or hanging anything: while
- * enabled, the multiply's launchers encode the tensor map of B with a box one row short, so
- * every stage receives fewer bytes than its mbarrier expects.  The kernels themselves are
+ * enabled, the multiply's launchers encode the tensor map of B (of A for the TF32 form that
+ * reads B with plain loads) with a box one row short, so every stage receives fewer bytes than
+ * its mbarrier expects.  The kernels themselves are
  * unchanged: each wait gives up after about a second of SM clock, the CTA leaves through
  * its barriers without storing, C keeps its contents and nmspmm_device_status reports
  * NMSPMM_DEVICE_TIMEOUT.  Returns the previous setting.  Process-wide; for tests only (use a

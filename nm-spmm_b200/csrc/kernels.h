@@ -102,7 +102,7 @@ inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), unsigned blocks, 
 }
 
 // Test hook (nmspmm_test_short_fill): non-zero makes the multiply launchers encode B's tensor
-// map with a box one row short.  The kernels are unchanged; their stages then never fill.
+// map (A's in gemm_tf32_expand.cu, which loads B without TMA) with a box one row short.  The kernels are unchanged; their stages then never fill.
 extern int g_test_short_fill;
 
 // packed = 0: scalar FFMA loop; 1: two-lane packed FFMA2 loop.
