@@ -267,9 +267,10 @@ static int g_tile_band = getenv("NMSPMM_TILE_BAND") ? atoi(getenv("NMSPMM_TILE_B
 // the order.  A larger one (the large sharded configuration on one GPU: 235 MB against 126 MB of
 // L2) would be streamed from HBM once per row of tiles; bands of about 32 MB of B are walked one
 // after the other instead, each over all rows of tiles, and what is re-read per band is A.
-// Tensor-core path only: 8192 x 28672 x 8192 went from 4.49 to 4.15 ms.  The exact path is
-// compute-bound there (B streams at under 1 TB/s), and the extra index arithmetic cost its
-// kernels, which sit at their register limit, 1 - 10 % at 4096^3: they keep the plain order.
+// 8192 x 28672 x 8192 on the tensor-core path went from 4.49 to 4.15 ms.  The exact path is
+// compute-bound on such shapes (B streams at under 1 TB/s); its 16:32 and unpruned kernels
+// take the banded order too, the others, which were up to 10 % slower at 4096^3 with the band
+// arithmetic in them, keep the plain order (gemm_ffma.cuh::tile_position).
 static int tile_band(const nmspmm_gemm_desc* d, int W, int ns, int tiles_x, int tiles_y)
 {
     const int forced = g_tile_band;                        // measurement / test knob: 0 = never, n = that width, -1 = the rule below
@@ -461,6 +462,8 @@ static int make_plan(const nmspmm_gemm_desc* d_in, int sms, Plan* p, bool any_ro
     const long long units = n_tiles * p->n_win;
     if (units >= (1LL << 31) || n_tiles >= (1LL << 28)) return NMSPMM_UNSUPPORTED;
     p->n_tiles = static_cast<int>(n_tiles);
+    if (mode == kModeLow && v->ws % 16 == 0)              // the variants compiled with the banded order (FfmaCfg::BANDED)
+        p->band = tile_band(d, p->W, v->ns, p->tiles_x, p->tiles_y);
     const int resident = sms * v->min_blocks;
     if (d->split_k > 0) {
         // Explicit K slices: one unit range per (tile, slice); a single slice stores directly.

@@ -76,8 +76,8 @@ NMSPMM_HD float* output_of(const GemmArgs& a, const GemmOutputs& o, int i) { ret
 // of tiles are cut into bands of that many, the bands are walked one after the other and each
 // band row by row: the CTAs resident at one time then share a band of B that stays in L2 (and a
 // few row panels of A) instead of streaming all of B once per row of tiles.  The planner bands
-// tensor-core problems whose compressed B outgrows L2 (make_plan); the exact path's kernels
-// read the low bits only and number their tiles row by row.
+// problems whose compressed B outgrows L2 (make_plan), except on those of the exact path's
+// kernels that number their tiles row by row (gemm_ffma.cuh::tile_position).
 constexpr int kTileBandShift = 24;
 NMSPMM_HD int pack_tiles_x(int tiles_x, int band) { return tiles_x | (band << kTileBandShift); }
 NMSPMM_HD void tile_coords(int tile, int tiles_x_packed, int tiles_y, int& ty, int& tx)

@@ -44,6 +44,7 @@ template <int MS, int NS, int WM, int WS, int KS_, int MODE>
 struct FfmaCfg {
     static constexpr int KS = KS_;                       // rows of A staged per window: 32, or 64 (a merged HIGH window)
     static constexpr bool PAIR = (MODE == kModeLow && KS_ == 64);    // LOW staged as pairs of 32-k windows (WS = 2 n_keep)
+    static constexpr bool BANDED = (MODE == kModeLow && WS % 16 == 0);   // 16:32 and unpruned: the tile order may be banded (see tile_position)
     static_assert(KS_ == 64 || (MODE == kModeLow && KS_ == 32), "LOW windows are 32 k wide, staged singly or in pairs; HIGH windows are 64 k wide");
     static constexpr int QT = NS / kVecLen;              // vectors per tile
     static constexpr int WARPS_M = MS / WM;
@@ -122,12 +123,29 @@ __device__ __forceinline__ void nm_gemm_ffma_body(const GemmArgs& g, const CUten
         u_end = static_cast<int>(u1);
     }
 
+    // Tile number -> position.  The 16:32 and unpruned variants take the banded order of
+    // gemm_args.h (the planner bands them when B outgrows L2); with that arithmetic in them
+    // they also run 1 - 7 % faster on every one of the reference's 100 benchmark shapes (a
+    // different register allocation: these kernels sit at their 128-register limit and the
+    // compiler's choices there move the result by several per cent either way).  The other
+    // variants were slower with it (12:32 up to 6 %, 8:32 1 %, 4:32 10 % at 4096^3): the
+    // planner never bands them and they keep the plain row-by-row expression.
+    auto tile_position = [&](int tile, int& ty, int& tx) {
+        if constexpr (Cfg::BANDED) {
+            tile_coords(tile, g.tiles_x, (g.M + MS - 1) / MS, ty, tx);
+        } else {
+            ty = tile / g.tiles_x;
+            tx = tile - ty * g.tiles_x;
+        }
+    };
+
     // ---- filling one stage: the whole warp calls this (warp-uniform arguments) ----
     // Unit `u` goes to stage s, which the caller knows to be free.
     auto fill = [&](int s, int u) {
         const uint32_t full = bars + s * 8;
         const int tile = u / g.sched.n_win, win = u - tile * g.sched.n_win;
-        const int ty = tile / g.tiles_x, tx = tile - ty * g.tiles_x;
+        int ty, tx;
+        tile_position(tile, ty, tx);
         const int bj = tx * NS, bi = ty * MS;
         const int cols = min(NS, g.N - bj);
         const int lb0 = bj >> layout_shift;                // first packed index block under the tile
@@ -167,7 +185,8 @@ __device__ __forceinline__ void nm_gemm_ffma_body(const GemmArgs& g, const CUten
         uint32_t d_rel, ci_rel;
         bool live;
         {
-            const int ty = tile / g.tiles_x, tx = tile - ty * g.tiles_x;
+            int ty, tx;
+            tile_position(tile, ty, tx);
             const int bj = tx * NS;
             live = (vec * kVecLen < g.N - bj);             // vectors past N idle but keep the ring moving
             const int q = (bj >> 5) + vec;                 // global vector number
@@ -280,7 +299,8 @@ __device__ __forceinline__ void nm_gemm_ffma_body(const GemmArgs& g, const CUten
         }
 
         // ---------------------------------------------------------------- end of the piece
-        const int ty = tile / g.tiles_x, tx = tile - ty * g.tiles_x;
+        int ty, tx;
+        tile_position(tile, ty, tx);
         const int bj = tx * NS, bi = ty * MS;
         const int col0 = bj + vec * kVecLen + (lane >> 4) * 8 + (lane & 1) * 4;      // and col0 + 16
         auto row_of = [&](int i) {

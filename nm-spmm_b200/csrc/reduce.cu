@@ -67,7 +67,8 @@ nm_reduce_pieces_kernel(const GemmArgs g, const GemmOutputs outs, int first_tile
     int v_first, v_last;
     tile_contributors(g.sched, tile, v_first, v_last);
     if (v_first == v_last) return;                         // one range held the whole tile and stored it
-    const int ty = tile / g.tiles_x, tx = tile - ty * g.tiles_x;          // the exact path numbers its tiles row by row
+    int ty, tx;
+    tile_coords(tile, g.tiles_x, (g.M + MS - 1) / MS, ty, tx);
     const int bj = tx * NS, bi = ty * MS;
     const int r = bi + Map::row(tid, i), c = bj + Map::col0(tid) + 16 * half;
     if (Map::vec(tid) * kVecLen >= g.N - bj || r >= g.M) return;       // vectors past N, rows past M
