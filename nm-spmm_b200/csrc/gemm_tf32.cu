@@ -49,6 +49,14 @@
 
 namespace nmspmm {
 
+// Diagnostic target, not part of the shipped library: built with
+//     NMSPMM_NVCC_EXTRA=-DNMSPMM_TF32_PROFILE NMSPMM_BUILD_DIR=<dir> NMSPMM_BUILD_LIB=<file.so> python nm-spmm_b200/build.py
+// the kernel adds up, per role, the cycles (clock64) spent waiting and issuing, and
+// nmspmm_debug_tf32_profile (exported by that build only) reads and clears the sixteen sums:
+//   0 producer waits for a free stage, 1 producer total, 2 / 3 / 4 / 5 gather issuer: wait for the
+//   stage, wait for a result buffer, issue, total, 6 / 7 / 15 product issuer: wait for the gather,
+//   issue, total, 8 CTAs, 9 steps, 13 / 14 epilogue: wait for the accumulators, run.
+// Without the macro every TF_* below expands to nothing.
 #ifdef NMSPMM_TF32_PROFILE
 __device__ unsigned long long g_tf32_profile[16];
 #define TF_DECL(...) long long __VA_ARGS__
