@@ -211,3 +211,64 @@ def test_tf32_forms_are_selected_by_tile_id(pkg):
     for tile in (pkg.TILE_128x256_GATHER, pkg.TILE_128x256_EXPAND):
         with pytest.raises(pkg.NMSpMMError):
             pkg.plan(pkg.make_desc(512, 1024, 1024, 16, pkg.FORMAT_LOW, 128, pkg.PATH_FP32, 0, tile))
+
+
+def test_banded_tile_order_visits_every_tile_once(tmp_path):
+    """gemm_args.h::tile_coords (shared by host and device): for plain and banded orders, full and
+    ragged last bands, every (row, column) of tiles is produced by exactly one tile number, tiles
+    of a band are consecutive, and band 0 is the row-by-row order."""
+    src = tmp_path / "order.cpp"
+    src.write_text(r'''
+#include <cstdio>
+#include <vector>
+#include "gemm_args.h"
+using namespace nmspmm;
+int main() {
+    const int shapes[][3] = {{5, 4, 0}, {5, 4, 2}, {112, 64, 16}, {7, 3, 3}, {8, 1, 4}, {9, 5, 127}, {33, 2, 8}, {224, 64, 32}};
+    for (auto& sh : shapes) {
+        const int tx_n = sh[0], ty_n = sh[1], band = sh[2];
+        if (band >= tx_n && band != 0) continue;               // the planner never packs a band that wide
+        const int packed = pack_tiles_x(tx_n, band);
+        std::vector<int> seen(tx_n * ty_n, 0);
+        int last_band = -1;
+        for (int t = 0; t < tx_n * ty_n; ++t) {
+            int ty, tx;
+            tile_coords(t, packed, ty_n, ty, tx);
+            if (ty < 0 || ty >= ty_n || tx < 0 || tx >= tx_n) { std::printf("range %d %d %d: tile %d -> %d %d\n", tx_n, ty_n, band, t, ty, tx); return 1; }
+            if (seen[ty * tx_n + tx]++) { std::printf("twice %d %d %d: tile %d\n", tx_n, ty_n, band, t); return 1; }
+            if (band == 0 && (ty != t / tx_n || tx != t % tx_n)) { std::printf("plain order broken at %d\n", t); return 1; }
+            if (band > 0) {
+                const int b = tx / band;
+                if (b < last_band) { std::printf("band order %d %d %d: tile %d\n", tx_n, ty_n, band, t); return 1; }
+                last_band = b;
+            }
+        }
+    }
+    std::printf("ok\n");
+    return 0;
+}
+''')
+    exe = tmp_path / "order"
+    inc = os.path.join(ROOT, "nm-spmm_b200", "csrc")
+    build = subprocess.run(["g++", "-std=c++17", "-O1", "-I", inc, str(src), "-o", str(exe)], capture_output=True, text=True)
+    assert build.returncode == 0, build.stderr
+    run = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert run.returncode == 0 and run.stdout.strip() == "ok", run.stdout + run.stderr
+
+
+def test_few_rows_plans(pkg):
+    """TF32 path, M <= 64: the library takes the 16 / 32 / 64-row tiles by itself, cuts K so that no
+    slice has more windows than a CTA's index list holds, and refuses what the form cannot do."""
+    for M, rows in ((1, 16), (16, 16), (17, 32), (32, 32), (33, 64), (64, 64)):
+        info = pkg.plan(pkg.make_desc(M + (-M) % 4, 11008, 4096, 8, pkg.FORMAT_HIGH, 128, pkg.PATH_TF32))
+        assert (info.tile_m, info.tile_n, info.threads) == (rows, 128, 128)
+        assert info.tiles_y == 1 and info.tiles_x == 86 and info.grid == 86 * info.split_k
+        assert -(-64 // info.split_k) <= 24                       # windows per slice (K / 64 = 64 merged windows)
+    assert pkg.plan(pkg.make_desc(68, 11008, 4096, 8, pkg.FORMAT_HIGH, 128, pkg.PATH_TF32)).tile_m == 128
+    deep = pkg.plan(pkg.make_desc(64, 1024, 131072, 4, pkg.FORMAT_HIGH, 128, pkg.PATH_TF32))
+    assert deep.tile_m == 64 and -(-2048 // deep.split_k) <= 24
+    lib = pkg.load_library()
+    too_few = pkg.make_desc(16, 1024, 131072, 4, pkg.FORMAT_HIGH, 128, pkg.PATH_TF32, 2, pkg.TILE_16x128)
+    assert lib.nmspmm_gemm_workspace_bytes(ctypes.byref(too_few)) == 0   # 1024 windows per slice: refused
+    # left to the library, the same split goes to the 128-row tiles instead
+    assert pkg.plan(pkg.make_desc(16, 1024, 131072, 4, pkg.FORMAT_HIGH, 128, pkg.PATH_TF32, 2)).tile_m == 128
